@@ -1,0 +1,374 @@
+// C ABI of libwinoconv_b200: descriptor validation, the DWM piece rule, scratch sizing and the
+// forward driver that walks the tiles in cache-sized blocks.  See include/winoconv_b200.h.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "wino_common.cuh"
+#include "wino_launch.h"
+
+namespace wino {
+namespace {
+
+thread_local std::string t_last_error;
+
+int fail(int status, const std::string &msg) {
+  t_last_error = msg;
+  return status;
+}
+
+int cuda_fail(cudaError_t e, const char *what, const char *detail = "") {
+  return fail(WINOCONV_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e) + (detail && *detail ? std::string(" (") + detail + ")" : std::string()));
+}
+
+size_t dtype_size(int dt) { return dt == WINOCONV_F32 ? 4 : 2; }
+
+// Per-dimension cut of a k-tap kernel into Winograd pieces: at multiples of 3, remainder last, and 4 -> 2 + 2
+// (the rule behind the look-up table of src/base_conv_launchers.h:58-388).
+void dwm_cuts(int taps, std::vector<std::pair<int, int>> &out) {
+  out.clear();
+  if (taps <= 3) { out.push_back({0, taps}); return; }
+  if (taps == 4) { out.push_back({0, 2}); out.push_back({2, 2}); return; }
+  for (int s = 0; s < taps; s += 3) out.push_back({s, std::min(3, taps - s)});
+}
+
+struct DimPiece { int phase, start, r; };
+
+struct Plan {
+  Geom g;
+  winoconv_plan_info_t info;
+  int dtype, product_dtype, engine;
+};
+
+// Working set the forward aims for (V block + M block), in bytes: small enough to stay in the 126 MB L2
+// between the three kernels of a pass.  A layer whose whole V + M fits kWholeBytesLimit runs as one pass.
+// WINOCONV_BLOCK_MB / WINOCONV_WHOLE_MB override them (read once) for tuning.
+unsigned long long env_mb(const char *name, unsigned long long dflt) {
+  const char *v = getenv(name);
+  if (!v || !*v) return dflt;
+  const long long mb = atoll(v);
+  return mb > 0 ? (unsigned long long)mb << 20 : dflt;
+}
+unsigned long long block_bytes_target() { static const unsigned long long v = env_mb("WINOCONV_BLOCK_MB", 48); return v; }
+unsigned long long whole_bytes_limit() { static const unsigned long long v = env_mb("WINOCONV_WHOLE_MB", 96); return v; }
+
+int build_plan(const winoconv_desc_t *d, Plan *plan) {
+  if (!d || !plan) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null descriptor");
+  if (d->ndim != 2 && d->ndim != 3) return fail(WINOCONV_ERR_UNSUPPORTED, "ndim must be 2 or 3");
+  if (d->batch <= 0 || d->c_in <= 0 || d->k_out <= 0) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "batch, c_in and k_out must be positive");
+  if (d->dtype < WINOCONV_F32 || d->dtype > WINOCONV_BF16) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "bad dtype");
+  if (d->weight_layout != WINOCONV_W_KCRS && d->weight_layout != WINOCONV_W_RSCK) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "bad weight_layout");
+  int pdt = d->product_dtype;
+  if (pdt != WINOCONV_F32 && pdt != d->dtype) return fail(WINOCONV_ERR_UNSUPPORTED, "product_dtype must be F32 or equal to dtype");
+  for (int i = 0; i < 3; ++i) {
+    const bool unused = (d->ndim == 2 && i == 0);
+    if (unused) {
+      if (d->in_size[0] > 1 || d->ker_size[0] > 1 || d->stride[0] > 1 || d->pad[0] != 0)
+        return fail(WINOCONV_ERR_INVALID_ARGUMENT, "ndim = 2 needs depth extent, kernel, stride <= 1 and pad 0");
+      continue;
+    }
+    if (d->in_size[i] <= 0) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "input extents must be positive");
+    if (d->ker_size[i] < 1 || d->ker_size[i] > 10) return fail(WINOCONV_ERR_UNSUPPORTED, "kernel extents must be 1..10");
+    if (d->stride[i] != 1 && d->stride[i] != 2) return fail(WINOCONV_ERR_UNSUPPORTED, "stride must be 1 or 2");
+    if (d->pad[i] < 0 || d->pad[i] > 64) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "bad padding");
+    if (d->in_size[i] + 2 * d->pad[i] < d->ker_size[i]) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "kernel larger than the padded input");
+  }
+  Geom &g = plan->g;
+  std::memset(&g, 0, sizeof(g));
+  std::memset(&plan->info, 0, sizeof(plan->info));
+  g.N = d->batch; g.C = d->c_in; g.K = d->k_out; g.Cp = (d->c_in + 7) / 8 * 8;
+  int in[3], ks[3], st[3], pd[3];
+  for (int i = 0; i < 3; ++i) {
+    const bool unused = (d->ndim == 2 && i == 0);
+    in[i] = unused ? 1 : d->in_size[i];
+    ks[i] = unused ? 1 : d->ker_size[i];
+    st[i] = unused ? 1 : d->stride[i];
+    pd[i] = unused ? 0 : d->pad[i];
+  }
+  // F(4x4,3x3): 2-D, 3x3, stride 1.  Auto picks it whenever it applies.
+  const bool f43_ok = ks[0] == 1 && in[0] == 1 && ks[1] == 3 && ks[2] == 3 && st[1] == 1 && st[2] == 1;
+  int tile_m = d->tile_m;
+  if (tile_m == 0) tile_m = f43_ok ? 4 : 2;
+  if (tile_m != 2 && tile_m != 4) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m must be 0, 2 or 4");
+  if (tile_m == 4 && !f43_ok) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 4 is F(4x4,3x3): 2-D, 3x3 kernel, stride 1 only");
+  int m[3], out[3], nt[3];
+  // A depth of one tap at stride 1 (every 2-D conv) is not tiled: no dummy F(2,1) along depth, which is
+  // what doubles the positions of every 2-D call in the reference (dwm.py:117).
+  m[0] = (ks[0] == 1 && st[0] == 1) ? 1 : 2;
+  m[1] = tile_m; m[2] = tile_m;
+  if (m[0] == 2 && tile_m == 4) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 4 with a depth kernel");
+  for (int i = 0; i < 3; ++i) {
+    out[i] = (in[i] + 2 * pd[i] - ks[i]) / st[i] + 1;
+    nt[i] = (out[i] + m[i] - 1) / m[i];
+  }
+  g.D = in[0]; g.H = in[1]; g.W = in[2];
+  g.oD = out[0]; g.oH = out[1]; g.oW = out[2];
+  g.nD = nt[0]; g.nH = nt[1]; g.nW = nt[2];
+  g.mD = m[0]; g.mH = m[1]; g.mW = m[2];
+  g.sD = st[0]; g.sH = st[1]; g.sW = st[2];
+  g.pD = pd[0]; g.pH = pd[1]; g.pW = pd[2];
+  g.kD = ks[0]; g.kH = ks[1]; g.kW = ks[2];
+  g.epilogue = d->epilogue;
+  g.weight_layout = d->weight_layout;
+  g.yD = g.oD; g.yH = g.oH; g.yW = g.oW;
+  if (d->epilogue & ~(WINOCONV_EPI_BIAS | WINOCONV_EPI_RELU | WINOCONV_EPI_POOL2)) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "unknown epilogue bits");
+  if (d->epilogue & WINOCONV_EPI_POOL2) {
+    if (m[0] != 1 || g.oD != 1) return fail(WINOCONV_ERR_UNSUPPORTED, "POOL2 is for 2-D convolutions");
+    if (g.oH < 2 || g.oW < 2) return fail(WINOCONV_ERR_UNSUPPORTED, "POOL2 needs at least a 2x2 output");
+    g.yH = g.oH / 2; g.yW = g.oW / 2;
+  }
+  // pieces: per dimension every (polyphase part, cut) pair; the product over dimensions, depth slowest
+  std::vector<DimPiece> per_dim[3];
+  std::vector<std::pair<int, int>> cuts;
+  for (int i = 0; i < 3; ++i) {
+    for (int phase = 0; phase < st[i]; ++phase) {
+      const int taps = (ks[i] - phase + st[i] - 1) / st[i];
+      if (taps <= 0) continue;
+      dwm_cuts(taps, cuts);
+      for (auto &c : cuts) per_dim[i].push_back({phase, c.first, c.second});
+    }
+  }
+  const size_t n_pieces = per_dim[0].size() * per_dim[1].size() * per_dim[2].size();
+  if (n_pieces > WINOCONV_MAX_PIECES) return fail(WINOCONV_ERR_UNSUPPORTED, "kernel decomposes into more than 64 pieces");
+  int pos = 0, np = 0;
+  for (auto &a : per_dim[0]) for (auto &b : per_dim[1]) for (auto &c : per_dim[2]) {
+    Piece &p = g.pieces[np++];
+    const DimPiece *dp[3] = {&a, &b, &c};
+    int n_pos = 1;
+    for (int i = 0; i < 3; ++i) {
+      p.phase[i] = (int8_t)dp[i]->phase; p.start[i] = (int8_t)dp[i]->start; p.r[i] = (int8_t)dp[i]->r;
+      n_pos *= (m[i] + dp[i]->r - 1);
+    }
+    p.type = (int8_t)((a.r - 1) * 9 + (b.r - 1) * 3 + (c.r - 1));
+    p.pos_base = (int16_t)pos; p.n_pos = (int16_t)n_pos;
+    pos += n_pos;
+  }
+  g.n_pieces = np; g.positions = pos;
+  g.T = (long long)g.N * g.nD * g.nH * g.nW;
+
+  int engine = d->gemm_engine;
+  if (engine == WINOCONV_GEMM_AUTO) engine = (d->dtype == WINOCONV_F32) ? WINOCONV_GEMM_SIMT : WINOCONV_GEMM_TCGEN05;
+  if (engine != WINOCONV_GEMM_SIMT && engine != WINOCONV_GEMM_TCGEN05) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "bad gemm_engine");
+  if (engine == WINOCONV_GEMM_TCGEN05 && d->dtype == WINOCONV_F32) return fail(WINOCONV_ERR_UNSUPPORTED, "the tcgen05 GEMM takes f16 / bf16; f32 runs on the SIMT GEMM");
+  plan->dtype = d->dtype; plan->product_dtype = pdt; plan->engine = engine;
+
+  winoconv_plan_info_t &I = plan->info;
+  for (int i = 0; i < 3; ++i) { I.conv_out_size[i] = out[i]; I.tile_m[i] = m[i]; I.tiles_per_dim[i] = nt[i]; }
+  I.out_size[0] = g.yD; I.out_size[1] = g.yH; I.out_size[2] = g.yW;
+  I.n_pieces = np; I.positions = pos; I.c_pad = g.Cp; I.gemm_engine = engine; I.tiles = g.T;
+  const unsigned long long esz = dtype_size(d->dtype), psz = dtype_size(pdt);
+  I.filter_bytes = (unsigned long long)pos * g.K * g.Cp * esz;
+  const unsigned long long v_tile = (unsigned long long)pos * g.Cp * esz, m_tile = (unsigned long long)pos * g.K * psz;
+  long long block = (long long)(block_bytes_target() / (v_tile + m_tile));
+  block = std::max(128LL, block / 128 * 128);
+  if ((unsigned long long)g.T * (v_tile + m_tile) <= whole_bytes_limit() || block > g.T) block = g.T;
+  I.block_tiles = block;
+  I.input_ws_bytes = v_tile * (unsigned long long)block;
+  I.product_ws_bytes = m_tile * (unsigned long long)block;
+  const long long min_block = std::min<long long>(128, g.T);
+  I.input_ws_bytes_min = v_tile * (unsigned long long)min_block;
+  I.product_ws_bytes_min = m_tile * (unsigned long long)min_block;
+  I.direct_flops = 2.0 * g.N * g.K * g.C * (double)ks[0] * ks[1] * ks[2] * (double)out[0] * out[1] * out[2];
+  I.gemm_flops = 2.0 * pos * (double)g.T * g.C * g.K;
+  I.algorithmic_bytes = (double)esz * ((double)g.N * g.D * g.H * g.W * g.C + (double)g.K * g.C * ks[0] * ks[1] * ks[2] +
+                                       (double)g.N * g.yD * g.yH * g.yW * g.K);
+  return WINOCONV_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int run_gemm(int dtype, int pdt, int engine, int positions, long long tiles, int c_pad, int k_out, const void *v,
+             const void *u, void *m, cudaStream_t s) {
+  if (engine == WINOCONV_GEMM_TCGEN05) {
+    const char *detail = "";
+    cudaError_t e = launch_gemm_tcgen05(dtype, pdt, positions, tiles, c_pad, k_out, v, u, m, s, &detail);
+    if (e != cudaSuccess) return cuda_fail(e, "tcgen05 GEMM launch", detail);
+    return WINOCONV_OK;
+  }
+  cudaError_t e = launch_gemm_simt(dtype, pdt, positions, tiles, c_pad, k_out, v, u, m, s);
+  if (e != cudaSuccess) return cuda_fail(e, "SIMT GEMM launch");
+  return WINOCONV_OK;
+}
+
+}  // namespace
+}  // namespace wino
+
+using namespace wino;
+
+extern "C" {
+
+int winoconv_abi_version(void) { return WINOCONV_ABI_VERSION; }
+
+const char *winoconv_status_string(int status) {
+  switch (status) {
+    case WINOCONV_OK: return "ok";
+    case WINOCONV_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case WINOCONV_ERR_UNSUPPORTED: return "unsupported configuration";
+    case WINOCONV_ERR_WORKSPACE: return "scratch buffer too small";
+    case WINOCONV_ERR_CUDA: return "CUDA error";
+    case WINOCONV_ERR_TIMEOUT: return "device-side wait timed out";
+    case WINOCONV_ERR_NO_DEVICE: return "no sm_100 device";
+    default: return "unknown status";
+  }
+}
+
+size_t winoconv_last_error(char *buf, size_t buf_size) {
+  if (buf && buf_size) {
+    const size_t n = std::min(buf_size - 1, t_last_error.size());
+    std::memcpy(buf, t_last_error.data(), n);
+    buf[n] = '\0';
+  }
+  return t_last_error.size();
+}
+
+int winoconv_device_check(void) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { cudaGetLastError(); return fail(WINOCONV_ERR_NO_DEVICE, std::string("cudaGetDevice: ") + cudaGetErrorString(e)); }
+  int major = 0;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) { cudaGetLastError(); return fail(WINOCONV_ERR_NO_DEVICE, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e)); }
+  if (major != 10) return fail(WINOCONV_ERR_NO_DEVICE, "the kernels are built for sm_100a only; current device has compute capability major " + std::to_string(major));
+  return WINOCONV_OK;
+}
+
+int winoconv_plan(const winoconv_desc_t *desc, winoconv_plan_info_t *info) {
+  if (!info) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null info");
+  Plan plan;
+  const int st = build_plan(desc, &plan);
+  if (st != WINOCONV_OK) return st;
+  *info = plan.info;
+  return WINOCONV_OK;
+}
+
+int winoconv_plan_pieces(const winoconv_desc_t *desc, int32_t *pieces, int32_t max_pieces, int32_t *n_pieces) {
+  if (!pieces || !n_pieces) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null output");
+  Plan plan;
+  const int st = build_plan(desc, &plan);
+  if (st != WINOCONV_OK) return st;
+  if (plan.g.n_pieces > max_pieces) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "pieces array too small");
+  for (int i = 0; i < plan.g.n_pieces; ++i)
+    for (int j = 0; j < 3; ++j) {
+      pieces[i * 9 + j] = plan.g.pieces[i].phase[j];
+      pieces[i * 9 + 3 + j] = plan.g.pieces[i].start[j];
+      pieces[i * 9 + 6 + j] = plan.g.pieces[i].r[j];
+    }
+  *n_pieces = plan.g.n_pieces;
+  return WINOCONV_OK;
+}
+
+int winoconv_filter_transform(const winoconv_desc_t *desc, const void *weights, void *u, void *stream) {
+  Plan plan;
+  int st = build_plan(desc, &plan);
+  if (st != WINOCONV_OK) return st;
+  if (!weights || !u) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null weights or u");
+  if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
+  cudaError_t e = launch_filter_transform(plan.g, plan.dtype, weights, u, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e, "filter transform launch");
+  return WINOCONV_OK;
+}
+
+int winoconv_forward(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias, void *y, void *v_ws,
+                     size_t v_ws_bytes, void *m_ws, size_t m_ws_bytes, void *stream) {
+  Plan plan;
+  int st = build_plan(desc, &plan);
+  if (st != WINOCONV_OK) return st;
+  if (!x || !u || !y || !v_ws || !m_ws) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null tensor or scratch pointer");
+  if ((desc->epilogue & WINOCONV_EPI_BIAS) && !bias) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "EPI_BIAS set but bias is null");
+  if (!aligned16(x) || !aligned16(u) || !aligned16(y) || !aligned16(v_ws) || !aligned16(m_ws))
+    return fail(WINOCONV_ERR_INVALID_ARGUMENT, "tensors and scratch must be 16-byte aligned");
+  if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
+  const Geom &g = plan.g;
+  const unsigned long long esz = dtype_size(plan.dtype), psz = dtype_size(plan.product_dtype);
+  const unsigned long long v_tile = (unsigned long long)g.positions * g.Cp * esz, m_tile = (unsigned long long)g.positions * g.K * psz;
+  long long block = (long long)std::min<unsigned long long>(v_ws_bytes / v_tile, m_ws_bytes / m_tile);
+  block = std::min(block, (long long)plan.info.block_tiles);  // never exceed the cache-sized block
+  if (block < std::min<long long>(128, g.T))
+    return fail(WINOCONV_ERR_WORKSPACE, "scratch holds " + std::to_string(block) + " tiles; need at least " +
+                                            std::to_string(std::min<long long>(128, g.T)) + " (see winoconv_plan)");
+  if (block < g.T) block = block / 128 * 128;
+  cudaStream_t s = (cudaStream_t)stream;
+  for (long long t0 = 0; t0 < g.T; t0 += block) {
+    const int n = (int)std::min<long long>(block, g.T - t0);
+    cudaError_t e = launch_input_transform(g, plan.dtype, x, v_ws, t0, n, s);
+    if (e != cudaSuccess) return cuda_fail(e, "input transform launch");
+    st = run_gemm(plan.dtype, plan.product_dtype, plan.engine, g.positions, n, g.Cp, g.K, v_ws, u, m_ws, s);
+    if (st != WINOCONV_OK) return st;
+    e = launch_output_transform(g, plan.dtype, plan.product_dtype, m_ws, y, bias, t0, n, s);
+    if (e != cudaSuccess) return cuda_fail(e, "output transform launch");
+  }
+  return WINOCONV_OK;
+}
+
+int winoconv_gemm_batched(int dtype, int product_dtype, int gemm_engine, int positions, int64_t tiles, int c_pad,
+                          int k_out, const void *v, const void *u, void *m, void *stream) {
+  if (!v || !u || !m) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null operand");
+  if (positions <= 0 || tiles <= 0 || c_pad <= 0 || k_out <= 0) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "sizes must be positive");
+  if (c_pad % 8 != 0) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "c_pad must be a multiple of 8");
+  if (dtype < WINOCONV_F32 || dtype > WINOCONV_BF16) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "bad dtype");
+  if (product_dtype != WINOCONV_F32 && product_dtype != dtype) return fail(WINOCONV_ERR_UNSUPPORTED, "product_dtype must be F32 or equal to dtype");
+  if (!aligned16(v) || !aligned16(u) || !aligned16(m)) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "operands must be 16-byte aligned");
+  int engine = gemm_engine;
+  if (engine == WINOCONV_GEMM_AUTO) engine = dtype == WINOCONV_F32 ? WINOCONV_GEMM_SIMT : WINOCONV_GEMM_TCGEN05;
+  if (engine == WINOCONV_GEMM_TCGEN05 && dtype == WINOCONV_F32) return fail(WINOCONV_ERR_UNSUPPORTED, "the tcgen05 GEMM takes f16 / bf16");
+  int st = winoconv_device_check();
+  if (st != WINOCONV_OK) return st;
+  return run_gemm(dtype, product_dtype, engine, positions, tiles, c_pad, k_out, v, u, m, (cudaStream_t)stream);
+}
+
+int winoconv_split(const float *x, float *out, int batch, int d, int h, int w, int c, int block_d, int block_h,
+                   int block_w, int out_block_d, int out_block_h, int out_block_w, int n_d, int n_h, int n_w,
+                   void *stream) {
+  if (!x || !out) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null tensor");
+  if (batch <= 0 || d <= 0 || h <= 0 || w <= 0 || c <= 0 || block_d <= 0 || block_h <= 0 || block_w <= 0 ||
+      out_block_d <= 0 || out_block_h <= 0 || out_block_w <= 0 || n_d <= 0 || n_h <= 0 || n_w <= 0)
+    return fail(WINOCONV_ERR_INVALID_ARGUMENT, "sizes must be positive");
+  if ((size_t)block_d * block_h * block_w * 33 * sizeof(float) > 48 * 1024)
+    return fail(WINOCONV_ERR_UNSUPPORTED, "tile volume too large for the split kernel (max 372 elements)");
+  int st = winoconv_device_check();
+  if (st != WINOCONV_OK) return st;
+  cudaError_t e = launch_split(x, out, batch, d, h, w, c, block_d, block_h, block_w, out_block_d, out_block_h,
+                               out_block_w, n_d, n_h, n_w, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e, "split launch");
+  return WINOCONV_OK;
+}
+
+int winoconv_concat(const float *tiles, float *y, int batch, int out_d, int out_h, int out_w, int k, int out_block_d,
+                    int out_block_h, int out_block_w, void *stream) {
+  if (!tiles || !y) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null tensor");
+  if (batch <= 0 || out_d <= 0 || out_h <= 0 || out_w <= 0 || k <= 0 || out_block_d <= 0 || out_block_h <= 0 || out_block_w <= 0)
+    return fail(WINOCONV_ERR_INVALID_ARGUMENT, "sizes must be positive");
+  if ((size_t)out_block_d * out_block_h * out_block_w * 33 * sizeof(float) > 48 * 1024)
+    return fail(WINOCONV_ERR_UNSUPPORTED, "output block too large for the concat kernel");
+  int st = winoconv_device_check();
+  if (st != WINOCONV_OK) return st;
+  cudaError_t e = launch_concat(tiles, y, batch, out_d, out_h, out_w, k, out_block_d, out_block_h, out_block_w, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e, "concat launch");
+  return WINOCONV_OK;
+}
+
+int winoconv_add(const float *a, const float *b, float *c, int64_t n, void *stream) {
+  if (n < 0) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "negative length");
+  if (n == 0) return WINOCONV_OK;
+  if (!a || !b || !c) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null tensor");
+  int st = winoconv_device_check();
+  if (st != WINOCONV_OK) return st;
+  cudaError_t e = launch_add(a, b, c, (long long)n, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e, "add launch");
+  return WINOCONV_OK;
+}
+
+int winoconv_read_device_error(void *stream, uint32_t *code) {
+  if (!code) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null code");
+  unsigned int host = 0;
+  cudaError_t e = read_and_clear_device_error((cudaStream_t)stream, &host);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the device error word");
+  *code = host;
+  if (host != 0) return fail(WINOCONV_ERR_TIMEOUT, "a bounded device wait gave up, code 0x" + [&] { char b[16]; snprintf(b, sizeof b, "%x", host); return std::string(b); }());
+  return WINOCONV_OK;
+}
+
+}  // extern "C"

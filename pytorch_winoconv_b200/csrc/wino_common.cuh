@@ -1,0 +1,240 @@
+// Shared device/host definitions of the Winograd / DWM engine: geometry passed by value to the
+// kernels, element-type helpers and the 1-D Cook-Toom transforms every kernel is built from.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "winoconv_b200.h"
+
+namespace wino {
+
+// One DWM piece: a sub-kernel of <= 3 taps per dimension, taken from polyphase part `phase`
+// of the kernel starting at tap `start` of that part.  The reference keeps the same table as
+// seven parallel int arrays copied to the device on every call
+// (base_conv_launchers.cu:323-336); here it rides in the kernel parameters.
+struct Piece {
+  int8_t phase[3];
+  int8_t start[3];
+  int8_t r[3];
+  int8_t type;       // (r_d - 1) * 9 + (r_h - 1) * 3 + (r_w - 1)
+  int16_t pos_base;  // first Winograd position of this piece
+  int16_t n_pos;     // alpha_d * alpha_h * alpha_w
+};
+
+struct Geom {
+  int N, C, K, Cp;
+  int D, H, W;          // input extents (unpadded)
+  int oD, oH, oW;       // convolution output extents
+  int yD, yH, yW;       // stored output extents (after pooling)
+  int nD, nH, nW;       // tiles per dimension
+  int mD, mH, mW;       // output block per dimension
+  int sD, sH, sW;       // stride
+  int pD, pH, pW;       // zero padding
+  int kD, kH, kW;       // kernel extents
+  int n_pieces;
+  int positions;
+  unsigned epilogue;
+  int weight_layout;
+  long long T;          // total tiles
+  Piece pieces[WINOCONV_MAX_PIECES];
+};
+
+// ------------------------------------------------------------------------------------------
+// element types
+// ------------------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float load(const float *p) { return *p; }
+  static __device__ __forceinline__ void store(float *p, float v) { *p = v; }
+};
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float load(const __half *p) { return __half2float(*p); }
+  static __device__ __forceinline__ void store(__half *p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+// VEC consecutive elements <-> VEC floats.  Addresses must be aligned to VEC * sizeof(T).
+template <typename T, int VEC> struct VecIO {
+  static __device__ __forceinline__ void load(const T *p, float (&v)[VEC]) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = Elem<T>::load(p + i);
+  }
+  static __device__ __forceinline__ void store(T *p, const float (&v)[VEC]) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) Elem<T>::store(p + i, v[i]);
+  }
+};
+template <> struct VecIO<float, 2> {
+  static __device__ __forceinline__ void load(const float *p, float (&v)[2]) {
+    float2 t = *reinterpret_cast<const float2 *>(p);
+    v[0] = t.x; v[1] = t.y;
+  }
+  static __device__ __forceinline__ void store(float *p, const float (&v)[2]) {
+    *reinterpret_cast<float2 *>(p) = make_float2(v[0], v[1]);
+  }
+};
+template <> struct VecIO<float, 4> {
+  static __device__ __forceinline__ void load(const float *p, float (&v)[4]) {
+    float4 t = *reinterpret_cast<const float4 *>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  static __device__ __forceinline__ void store(float *p, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct VecIO<__half, 2> {
+  static __device__ __forceinline__ void load(const __half *p, float (&v)[2]) {
+    float2 t = __half22float2(*reinterpret_cast<const __half2 *>(p));
+    v[0] = t.x; v[1] = t.y;
+  }
+  static __device__ __forceinline__ void store(__half *p, const float (&v)[2]) {
+    *reinterpret_cast<__half2 *>(p) = __floats2half2_rn(v[0], v[1]);
+  }
+};
+template <> struct VecIO<__half, 4> {
+  static __device__ __forceinline__ void load(const __half *p, float (&v)[4]) {
+    uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+    float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+  static __device__ __forceinline__ void store(__half *p, const float (&v)[4]) {
+    uint2 raw;
+    *reinterpret_cast<__half2 *>(&raw.x) = __floats2half2_rn(v[0], v[1]);
+    *reinterpret_cast<__half2 *>(&raw.y) = __floats2half2_rn(v[2], v[3]);
+    *reinterpret_cast<uint2 *>(p) = raw;
+  }
+};
+template <> struct VecIO<__nv_bfloat16, 2> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&v)[2]) {
+    float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+    v[0] = t.x; v[1] = t.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[2]) {
+    *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(v[0], v[1]);
+  }
+};
+template <> struct VecIO<__nv_bfloat16, 4> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&v)[4]) {
+    uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[4]) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2 *>(p) = raw;
+  }
+};
+
+// ------------------------------------------------------------------------------------------
+// 1-D Cook-Toom transforms F(M, R), alpha = M + R - 1.
+//   bt: data     d[alpha] -> v[alpha]   (B^T d)
+//   g : filter   w[R]     -> u[alpha]   (G w)
+//   at: product  p[alpha] -> y[M]       (A^T p)
+// F(2,1), F(2,2), F(2,3) follow the matrices (and signs) of the reference
+// (calculation_kernels.cu:12-41,773-802,1534-1551 == matrix_conv.py:15-30); F(4,3) is the
+// Cook-Toom triple on the points (0, 1, -1, 2, -2, inf).  Arrays are accessed with a
+// compile-time stride so the callers can keep whole patches in registers.
+// ------------------------------------------------------------------------------------------
+template <int M, int R> struct Xf;
+
+template <> struct Xf<1, 1> {
+  static constexpr int ALPHA = 1;
+  template <int S> static __device__ __forceinline__ void bt(float *) {}
+  template <int SI, int SO> static __device__ __forceinline__ void g(const float *w, float *u) { u[0] = w[0]; }
+  template <int SI, int SO> static __device__ __forceinline__ void at(const float *p, float *y) { y[0] = p[0]; }
+};
+
+template <> struct Xf<2, 1> {
+  static constexpr int ALPHA = 2;
+  template <int S> static __device__ __forceinline__ void bt(float *) {}
+  template <int SI, int SO> static __device__ __forceinline__ void g(const float *w, float *u) {
+    u[0] = w[0]; u[SO] = w[0];
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void at(const float *p, float *y) {
+    y[0] = p[0]; y[SO] = p[SI];
+  }
+};
+
+template <> struct Xf<2, 2> {
+  static constexpr int ALPHA = 3;
+  template <int S> static __device__ __forceinline__ void bt(float *d) {
+    float d1 = d[S];
+    d[0] = d[0] - d1;
+    d[2 * S] = d[2 * S] - d1;
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void g(const float *w, float *u) {
+    float w0 = w[0], w1 = w[SI];
+    u[0] = w0; u[SO] = w0 + w1; u[2 * SO] = w1;
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void at(const float *p, float *y) {
+    float p0 = p[0], p1 = p[SI], p2 = p[2 * SI];
+    y[0] = p0 + p1; y[SO] = p1 + p2;
+  }
+};
+
+template <> struct Xf<2, 3> {
+  static constexpr int ALPHA = 4;
+  template <int S> static __device__ __forceinline__ void bt(float *d) {
+    float d0 = d[0], d1 = d[S], d2 = d[2 * S], d3 = d[3 * S];
+    d[0] = d0 - d2; d[S] = d1 + d2; d[2 * S] = d2 - d1; d[3 * S] = d1 - d3;
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void g(const float *w, float *u) {
+    float w0 = w[0], w1 = w[SI], w2 = w[2 * SI];
+    float s = 0.5f * (w0 + w2);
+    u[0] = w0; u[SO] = s + 0.5f * w1; u[2 * SO] = s - 0.5f * w1; u[3 * SO] = w2;
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void at(const float *p, float *y) {
+    float p0 = p[0], p1 = p[SI], p2 = p[2 * SI], p3 = p[3 * SI];
+    y[0] = p0 + p1 + p2; y[SO] = p1 - p2 - p3;
+  }
+};
+
+template <> struct Xf<4, 3> {
+  static constexpr int ALPHA = 6;
+  template <int S> static __device__ __forceinline__ void bt(float *d) {
+    float d0 = d[0], d1 = d[S], d2 = d[2 * S], d3 = d[3 * S], d4 = d[4 * S], d5 = d[5 * S];
+    float a = fmaf(-4.f, d2, d4);       // d4 - 4 d2
+    float b = fmaf(-4.f, d1, d3);       // d3 - 4 d1
+    float c = d4 - d2;
+    float e = 2.f * (d3 - d1);
+    d[0] = fmaf(4.f, d0, fmaf(-5.f, d2, d4));
+    d[S] = a + b;
+    d[2 * S] = a - b;
+    d[3 * S] = c + e;
+    d[4 * S] = c - e;
+    d[5 * S] = fmaf(4.f, d1, fmaf(-5.f, d3, d5));
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void g(const float *w, float *u) {
+    float w0 = w[0], w1 = w[SI], w2 = w[2 * SI];
+    float s = w0 + w2;
+    float t = fmaf(4.f, w2, w0);
+    u[0] = 0.25f * w0;
+    u[SO] = -(s + w1) * (1.f / 6.f);
+    u[2 * SO] = -(s - w1) * (1.f / 6.f);
+    u[3 * SO] = fmaf(2.f, w1, t) * (1.f / 24.f);
+    u[4 * SO] = fmaf(-2.f, w1, t) * (1.f / 24.f);
+    u[5 * SO] = w2;
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void at(const float *p, float *y) {
+    float p0 = p[0], p1 = p[SI], p2 = p[2 * SI], p3 = p[3 * SI], p4 = p[4 * SI], p5 = p[5 * SI];
+    float s12 = p1 + p2, d12 = p1 - p2, s34 = p3 + p4, d34 = p3 - p4;
+    y[0] = p0 + s12 + s34;
+    y[SO] = fmaf(2.f, d34, d12);
+    y[2 * SO] = fmaf(4.f, s34, s12);
+    y[3 * SO] = fmaf(8.f, d34, d12) + p5;
+  }
+};
+
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace wino

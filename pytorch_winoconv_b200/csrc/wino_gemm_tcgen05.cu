@@ -1,0 +1,374 @@
+// Per-position batched GEMM on the 5th-generation tensor cores (sm_100a):
+//
+//     m[p][t][k] = sum_c v[p][t][c] * u[p][k][c]        fp16 / bf16 in, fp32 accumulate
+//
+// One CTA computes a 128 (tiles) x BN (output channels) block of one Winograd position.
+//   warp 0      TMA producer: cp.async.bulk.tensor.3d loads of the V slab [128 x 64] and the U slab
+//               [BN x 64] (both reduction-major, 128-byte swizzle) into a ring of shared-memory stages,
+//               completion on an mbarrier per stage.  No cluster, no multicast.
+//   warp 1      owns TMEM (tcgen05.alloc / dealloc) and issues tcgen05.mma.cta_group::1.kind::f16
+//               from one thread: four K=16 MMAs per 64-wide slab, accumulator 128 lanes x BN fp32 columns
+//               in TMEM; tcgen05.commit hands each stage back to the producer and finally signals the
+//               epilogue.
+//   warps 2..5  epilogue: tcgen05.ld of their 32-lane quarter, 32 columns at a time, transposed through
+//               shared memory (the stage ring is idle by then) so that each store instruction writes whole
+//               128-byte rows of M.
+// Ragged edges need no special code on the load side: TMA zero-fills rows beyond `tiles` / `k_out` and
+// channels beyond `c_pad`; the epilogue masks its stores.
+//
+// Every mbarrier wait is bounded (about a second of SM clocks).  A wait that gives up records a code in
+// g_device_error, raises the CTA's abort word so the other roles stop too, and the CTA still frees its
+// TMEM and returns.
+//
+// Stands in for forwardAssign + cublasHgemmBatched (src/base_conv_launchers_half.cu:218-236; the
+// reference accumulates in fp16 there) and cublasSgemmBatched (src/base_conv_launchers.cu:349-367).
+#include <cuda.h>
+
+#include "wino_common.cuh"
+#include "wino_launch.h"
+
+namespace wino {
+
+// Error word of the bounded waits (0 = none).  Lives in this translation unit with its only writers.
+__device__ unsigned int g_device_error = 0;
+
+namespace tc {
+
+constexpr int BM = 128;      // rows (tiles) per CTA == TMEM lanes
+constexpr int BK = 64;       // reduction slab: 64 x 2 B = one 128-byte swizzle row
+constexpr int UMMA_K = 16;   // reduction depth of one kind::f16 MMA
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;  // ~1 s at 1.9 GHz
+
+enum ErrCode : unsigned { ERR_PRODUCER_EMPTY = 0x101, ERR_MMA_FULL = 0x102, ERR_EPI_ACC = 0x103, ERR_DRAIN = 0x104 };
+
+template <int BN> struct Cfg {
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static_assert(RING_BYTES >= 4 * 32 * 36 * 4, "epilogue staging must fit in the ring");
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the CTA is aborting or the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_word != 0u) return false;
+    if (clock64() - start > WAIT_LIMIT_CLOCKS) {
+      *abort_word = code;
+      atomicCAS(&g_device_error, 0u, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: reduction-major operand, 128-byte swizzle, rows 128 B apart, groups of
+// eight rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <typename TM> struct StoreRow;
+// 8 lanes x float4 cover the 32 columns of one row; 4 rows per instruction.
+template <> struct StoreRow<float> {
+  static constexpr int ROWS_PER_ITER = 4;
+  static __device__ __forceinline__ void run(const float *stage, int lane, int iter, float *m_rows, long long ld,
+                                             int rows_valid, int cols_valid) {
+    const int r = iter * 4 + (lane >> 3), c = (lane & 7) * 4;
+    if (r < rows_valid && c < cols_valid) {
+      const float4 val = *reinterpret_cast<const float4 *>(stage + r * 36 + c);
+      *reinterpret_cast<float4 *>(m_rows + r * ld + c) = val;
+    }
+  }
+};
+// 4 lanes x 8 values (16 bytes of 16-bit output) cover one row; 8 rows per instruction.
+template <typename H> struct StoreRow16 {
+  static constexpr int ROWS_PER_ITER = 8;
+  static __device__ __forceinline__ void run(const float *stage, int lane, int iter, H *m_rows, long long ld,
+                                             int rows_valid, int cols_valid) {
+    const int r = iter * 8 + (lane >> 2), c = (lane & 3) * 8;
+    if (r < rows_valid && c < cols_valid) {
+      const float4 a = *reinterpret_cast<const float4 *>(stage + r * 36 + c);
+      const float4 b = *reinterpret_cast<const float4 *>(stage + r * 36 + c + 4);
+      float v[4] = {a.x, a.y, a.z, a.w}, w[4] = {b.x, b.y, b.z, b.w};
+      VecIO<H, 4>::store(m_rows + r * ld + c, v);
+      VecIO<H, 4>::store(m_rows + r * ld + c + 4, w);
+    }
+  }
+};
+template <> struct StoreRow<__half> : StoreRow16<__half> {};
+template <> struct StoreRow<__nv_bfloat16> : StoreRow16<__nv_bfloat16> {};
+
+template <int BN, typename TM>
+__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_v,
+                                                               const __grid_constant__ CUtensorMap map_u,
+                                                               TM *__restrict__ m, int tiles, int c_pad, int k_out,
+                                                               int n_blocks, uint32_t idesc) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzled stages need 1024-byte alignment
+  uint8_t *ring_ptr = smem_raw + (ring - raw);
+  const uint32_t bars = ring + C::RING_BYTES;    // full[STAGES], empty[STAGES], acc_full
+  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(ring_ptr + C::RING_BYTES + 128);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ring_ptr + C::RING_BYTES + 132);
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * C::STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_blk = blockIdx.x % n_blocks, m_blk = blockIdx.x / n_blocks, pos = blockIdx.y;
+  const int n_kb = (c_pad + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_word = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // whole warp: allocate BN fp32 accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < n_kb; ++kb) {
+        const int s = kb % C::STAGES;
+        const uint32_t ph = (uint32_t)(kb / C::STAGES) & 1u;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) break;
+        mbar_expect_tx(full_bar(s), (uint32_t)C::STAGE_BYTES);
+        const uint32_t a_dst = ring + s * C::STAGE_BYTES;
+        tma_load_3d(a_dst, &map_v, full_bar(s), kb * BK, m_blk * BM, pos);
+        tma_load_3d(a_dst + A_STAGE_BYTES, &map_u, full_bar(s), kb * BK, n_blk * BN, pos);
+        issued = kb + 1;
+      }
+      if (*abort_word != 0u) {
+        // Aborting: nobody may be consuming any more.  Wait (bounded) until every load this thread issued
+        // has landed, so no bulk copy is still writing shared memory when the CTA exits.
+        for (int kb = (issued > C::STAGES ? issued - C::STAGES : 0); kb < issued; ++kb) {
+          const long long start = clock64();
+          while (!mbar_try_wait(full_bar(kb % C::STAGES), (uint32_t)(kb / C::STAGES) & 1u)) {
+            if (clock64() - start > WAIT_LIMIT_CLOCKS) { atomicCAS(&g_device_error, 0u, (unsigned)ERR_DRAIN); break; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < n_kb && ok; ++kb) {
+        const int s = kb % C::STAGES;
+        const uint32_t ph = (uint32_t)(kb / C::STAGES) & 1u;
+        ok = mbar_wait(full_bar(s), ph, abort_word, ERR_MMA_FULL);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_base = ring + s * C::STAGE_BYTES;
+        const uint64_t adesc = make_smem_desc(a_base);
+        const uint64_t bdesc = make_smem_desc(a_base + A_STAGE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // advancing 16 elements along the reduction = 32 bytes = 2 descriptor address units
+          umma_f16(tmem_acc, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));  // stage reusable once these MMAs have read it
+      }
+      umma_commit(acc_bar);         // accumulator complete (or whatever was issued, when aborting)
+    }
+  }
+  __syncwarp();
+
+  if (warp >= 2) {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    unsigned got = 0;
+    if (lane == 0) got = mbar_wait(acc_bar, 0u, abort_word, ERR_EPI_ACC) ? 1u : 0u;
+    got = __shfl_sync(0xffffffffu, got, 0);
+    const bool healthy = got != 0u && *abort_word == 0u;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float *stage = reinterpret_cast<float *>(ring_ptr) + (warp - 2) * (32 * 36);
+    const long long row0 = (long long)m_blk * BM + q * 32;
+    const int rows_valid = (int)max(0LL, min(32LL, (long long)tiles - row0));
+    TM *m_rows = m + ((long long)pos * tiles + row0) * k_out + (long long)n_blk * BN;
+    const bool vec_ok = (k_out % 8) == 0;
+    if (healthy) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int cols_valid = min(32, k_out - (n_blk * BN + c0));
+        if (cols_valid <= 0) break;   // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4 *>(stage + lane * 36 + 4 * j) =
+              make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                          __uint_as_float(r[4 * j + 3]));
+        __syncwarp();
+        if (vec_ok) {
+#pragma unroll
+          for (int it = 0; it < 32 / StoreRow<TM>::ROWS_PER_ITER; ++it)
+            StoreRow<TM>::run(stage, lane, it, m_rows + c0, (long long)k_out, rows_valid, cols_valid);
+        } else {  // k_out not a multiple of 8: rows of M are not 16-byte aligned, store element-wise
+          for (int rr = 0; rr < rows_valid; ++rr)
+            if (lane < cols_valid) Elem<TM>::store(m_rows + (long long)rr * k_out + c0 + lane, stage[rr * 36 + lane]);
+        }
+        __syncwarp();
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows x c_pad operand per position, reduction innermost: dims {c_pad, rows, positions}.
+static bool make_operand_map(CUtensorMap *map, int dtype, const void *base, int c_pad, long long rows, int positions,
+                             int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)c_pad, (cuuint64_t)rows, (cuuint64_t)positions};
+  const cuuint64_t strides[2] = {(cuuint64_t)c_pad * 2ull, (cuuint64_t)c_pad * 2ull * (cuuint64_t)rows};
+  const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUtensorMapDataType dt = dtype == WINOCONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return enc(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, typename TM>
+static cudaError_t run(int dtype, int positions, long long tiles, int c_pad, int k_out, const void *v, const void *u,
+                       void *m, cudaStream_t s, const char **detail) {
+  using C = Cfg<BN>;
+  CUtensorMap map_v, map_u;
+  if (!make_operand_map(&map_v, dtype, v, c_pad, tiles, positions, BM) ||
+      !make_operand_map(&map_u, dtype, u, c_pad, k_out, positions, BN)) {
+    *detail = "cuTensorMapEncodeTiled failed (operands must be 16-byte aligned, c_pad a multiple of 8)";
+    return cudaErrorInvalidValue;
+  }
+  auto kern = gemm_tcgen05_kernel<BN, TM>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
+  const int n_blocks = (k_out + BN - 1) / BN;
+  const long long m_blocks = (tiles + BM - 1) / BM;
+  if (m_blocks * n_blocks > 0x7fffffffLL) { *detail = "too many tile blocks for one launch"; return cudaErrorInvalidConfiguration; }
+  // instruction descriptor: D = f32, A = B = f16 (0) or bf16 (1), both reduction-major, N >> 3, M >> 4
+  const uint32_t fmt = dtype == WINOCONV_F16 ? 0u : 1u;
+  const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  dim3 grid((unsigned)(m_blocks * n_blocks), (unsigned)positions), block(192);
+  kern<<<grid, block, C::SMEM_BYTES, s>>>(map_v, map_u, (TM *)m, (int)tiles, c_pad, k_out, n_blocks, idesc);
+  return cudaGetLastError();
+}
+
+template <typename TM>
+static cudaError_t pick_bn(int dtype, int positions, long long tiles, int c_pad, int k_out, const void *v,
+                           const void *u, void *m, cudaStream_t s, const char **detail) {
+  if (k_out <= 64) return run<64, TM>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  if (k_out <= 128) return run<128, TM>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  return run<256, TM>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+}
+
+}  // namespace tc
+
+cudaError_t read_and_clear_device_error(cudaStream_t s, unsigned int *code) {
+  unsigned int host = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(&host, g_device_error, sizeof(host), 0, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaMemcpyToSymbolAsync(g_device_error, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  *code = host;
+  return e;
+}
+
+cudaError_t launch_gemm_tcgen05(int dtype, int product_dtype, int positions, long long tiles, int c_pad, int k_out,
+                                const void *v, const void *u, void *m, cudaStream_t s, const char **detail) {
+  *detail = "";
+  if (positions <= 0 || tiles <= 0) return cudaSuccess;
+  if (dtype != WINOCONV_F16 && dtype != WINOCONV_BF16) { *detail = "tcgen05 GEMM takes f16 or bf16 operands"; return cudaErrorInvalidValue; }
+  if (c_pad % 8 != 0 || positions > 65535 || tiles > 0x7fffffffLL) { *detail = "c_pad must be a multiple of 8; positions <= 65535"; return cudaErrorInvalidValue; }
+  if (product_dtype == WINOCONV_F32) return tc::pick_bn<float>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  if (dtype == WINOCONV_F16) return tc::pick_bn<__half>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  return tc::pick_bn<__nv_bfloat16>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+}
+
+}  // namespace wino

@@ -1,0 +1,31 @@
+// Host-side launch functions shared between the translation units of libwinoconv_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "wino_common.cuh"
+
+namespace wino {
+
+cudaError_t launch_filter_transform(const Geom &g, int dtype, const void *w, void *u, cudaStream_t s);
+cudaError_t launch_input_transform(const Geom &g, int dtype, const void *x, void *v, long long t0, int n_tiles,
+                                   cudaStream_t s);
+cudaError_t launch_output_transform(const Geom &g, int dtype, int product_dtype, const void *m, void *y,
+                                    const void *bias, long long t0, int n_tiles, cudaStream_t s);
+cudaError_t launch_split(const float *x, float *out, int N, int D, int H, int W, int C, int bD, int bH, int bW,
+                         int oD, int oH, int oW, int nD, int nH, int nW, cudaStream_t s);
+cudaError_t launch_concat(const float *tiles, float *y, int N, int oD, int oH, int oW, int K, int mD, int mH, int mW,
+                          cudaStream_t s);
+cudaError_t launch_add(const float *a, const float *b, float *c, long long n, cudaStream_t s);
+
+// m[p][t][k] = sum_c v[p][t][c] u[p][k][c]; fp32 accumulate.
+cudaError_t launch_gemm_simt(int dtype, int product_dtype, int positions, long long tiles, int c_pad, int k_out,
+                             const void *v, const void *u, void *m, cudaStream_t s);
+// tcgen05 / TMEM / TMA version (f16 / bf16).  `detail` receives a message on failure.
+cudaError_t launch_gemm_tcgen05(int dtype, int product_dtype, int positions, long long tiles, int c_pad, int k_out,
+                                const void *v, const void *u, void *m, cudaStream_t s, const char **detail);
+
+// Reads the error word of the bounded device waits, clears it and synchronises the stream.
+cudaError_t read_and_clear_device_error(cudaStream_t s, unsigned int *code);
+
+}  // namespace wino

@@ -1,0 +1,144 @@
+"""Host-side checks that need no GPU: the C-ABI library loads, exports every symbol the header
+declares, plans shapes the way the oracle's restatement of the reference does, and reports
+errors as status codes instead of exiting the process."""
+import os
+import re
+
+import pytest
+import torch
+
+from oracle import winograd_oracle as wo
+from pytorch_winoconv_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "winoconv_b200.h")).read()
+    declared = set(re.findall(r"WINOCONV_API\s+[\w\s\*]+?\b(winoconv_\w+)\s*\(", header))
+    assert declared == set(capi.EXPORTED_SYMBOLS)
+    L = capi.lib()
+    for name in declared:
+        assert getattr(L, name) is not None
+    assert L.winoconv_abi_version() == 1
+    assert L.winoconv_status_string(capi.ERR_UNSUPPORTED) == b"unsupported configuration"
+
+
+BASELINE_CONFIGS = [
+    # name, kwargs, expected (positions, pieces, tiles)
+    ("cfg1", dict(ndim=2, batch=8, c_in=64, k_out=64, in_size=(56, 56), ker_size=3, pad=1, tile_m=2, dtype=capi.F32), (16, 1, 6272)),
+    ("cfg2", dict(ndim=2, batch=32, c_in=256, k_out=256, in_size=(28, 28), ker_size=3, pad=1, tile_m=4), (36, 1, 1568)),
+    ("cfg3a", dict(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3), (100, 9, 200704)),
+    ("cfg3b", dict(ndim=2, batch=32, c_in=128, k_out=128, in_size=(56, 56), ker_size=5, pad=2), (49, 4, 25088)),
+    ("cfg4", dict(ndim=3, batch=8, c_in=64, k_out=64, in_size=(16, 56, 56), ker_size=3, pad=1), (64, 1, 50176)),
+]
+
+
+@pytest.mark.parametrize("name,kw,expect", BASELINE_CONFIGS)
+def test_plan_matches_survey_figures(name, kw, expect):
+    info = capi.plan(capi.make_desc(**kw))
+    assert (info.positions, info.n_pieces, info.tiles) == expect
+    d = capi.make_desc(**kw)
+    n_out = 1
+    for o in info.conv_out_size:
+        n_out *= o
+    ks = 1
+    for k in d.ker_size:
+        ks *= k
+    assert info.direct_flops == pytest.approx(2.0 * d.batch * d.k_out * d.c_in * ks * n_out)
+    assert info.gemm_flops == pytest.approx(2.0 * info.positions * info.tiles * d.c_in * d.k_out)
+
+
+@pytest.mark.parametrize("ks,stride", [((5, 5), 1), ((7, 7), 1), ((7, 7), 2), ((9, 9), 1), ((4, 4), 1), ((3, 4), 1),
+                                       ((10, 3), 1), ((8, 4), 1), ((3, 3), 2), ((1, 1), 1), ((2, 2), 1)])
+def test_piece_table_matches_oracle_rule(ks, stride):
+    d = capi.make_desc(ndim=2, batch=1, c_in=8, k_out=8, in_size=(32, 32), ker_size=ks, stride=stride, tile_m=2)
+    got = capi.plan_pieces(d)
+    want = wo.dwm_pieces((1,) + ks, (1, stride, stride))
+    want = [(tuple(p[0] for p in piece), tuple(p[1] for p in piece), tuple(p[2] for p in piece)) for piece in want]
+    assert got == want
+
+
+def test_piece_table_3d():
+    d = capi.make_desc(ndim=3, batch=1, c_in=8, k_out=8, in_size=(12, 12, 12), ker_size=(5, 7, 7))
+    got = capi.plan_pieces(d)
+    want = wo.dwm_pieces((5, 7, 7), (1, 1, 1))
+    assert len(got) == len(want) == 18
+    assert [g[2] for g in got] == [tuple(p[2] for p in piece) for piece in want]
+
+
+def test_tile_counts_and_output_sizes():
+    info = capi.plan(capi.make_desc(ndim=2, batch=2, c_in=8, k_out=8, in_size=(13, 10), ker_size=3, pad=1, tile_m=4))
+    assert list(info.out_size) == [1, 13, 10] and list(info.tiles_per_dim) == [1, 4, 3] and info.tiles == 24
+    info = capi.plan(capi.make_desc(ndim=2, batch=2, c_in=8, k_out=8, in_size=(13, 10), ker_size=3, pad=1,
+                                    epilogue=capi.EPI_POOL2 | capi.EPI_RELU))
+    assert list(info.out_size) == [1, 6, 5] and list(info.conv_out_size) == [1, 13, 10]
+    info = capi.plan(capi.make_desc(ndim=2, batch=1, c_in=3, k_out=8, in_size=(224, 224), ker_size=7, stride=2, pad=3))
+    assert list(info.out_size) == [1, 112, 112] and info.c_pad == 8
+
+
+@pytest.mark.parametrize("kw,status", [
+    (dict(ndim=4), capi.ERR_UNSUPPORTED),
+    (dict(ker_size=11), capi.ERR_UNSUPPORTED),
+    (dict(stride=3), capi.ERR_UNSUPPORTED),
+    (dict(tile_m=4, ker_size=5), capi.ERR_UNSUPPORTED),
+    (dict(tile_m=3), capi.ERR_UNSUPPORTED),
+    (dict(batch=0), capi.ERR_INVALID_ARGUMENT),
+    (dict(dtype=7), capi.ERR_INVALID_ARGUMENT),
+    (dict(in_size=(2, 2), ker_size=5), capi.ERR_INVALID_ARGUMENT),
+    (dict(dtype=capi.F32, gemm_engine=capi.GEMM_TCGEN05), capi.ERR_UNSUPPORTED),
+    (dict(dtype=capi.F16, product_dtype=capi.BF16), capi.ERR_UNSUPPORTED),
+    (dict(epilogue=64), capi.ERR_INVALID_ARGUMENT),
+])
+def test_bad_descriptors_return_status_not_exit(kw, status):
+    base = dict(ndim=2, batch=1, c_in=8, k_out=8, in_size=(16, 16), ker_size=3)
+    base.update(kw)
+    if base["ndim"] == 4:
+        d = capi.make_desc(**{**base, "ndim": 2})
+        d.ndim = 4
+    else:
+        d = capi.make_desc(**base)
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.plan(d)
+    assert ei.value.status == status
+    assert str(ei.value)
+
+
+def test_null_pointers_rejected_before_any_device_call():
+    d = capi.make_desc(ndim=2, batch=1, c_in=8, k_out=8, in_size=(16, 16), ker_size=3)
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.forward(d, None, None, None, None, None, 0, None, 0)
+    assert ei.value.status == capi.ERR_INVALID_ARGUMENT
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.gemm_batched(capi.F16, capi.F32, capi.GEMM_AUTO, 1, 1, 12, 8, 16, 16, 16)
+    assert ei.value.status == capi.ERR_INVALID_ARGUMENT   # c_pad not a multiple of 8
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU error path")
+def test_no_device_is_an_error_not_a_fallback():
+    d = capi.make_desc(ndim=2, batch=1, c_in=8, k_out=8, in_size=(16, 16), ker_size=3)
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.filter_transform(d, 16, 16)
+    assert ei.value.status == capi.ERR_NO_DEVICE
+    from pytorch_winoconv_b200 import engine
+    with pytest.raises(RuntimeError):
+        engine.WinoConv((1, 16, 16, 8), torch.zeros(8, 8, 3, 3))
+
+
+def test_reference_named_modules_import():
+    import MakePytorchPlusPlus as mpp
+    import MakePytorchBackend as backend
+    assert set(mpp.__all__) == {"AddGPU", "Foo", "WinoSplit", "WinoConcat", "DWM", "add_gpu", "wino_split", "wino_concat"}
+    f = backend.Foo()
+    f.setKey(7)
+    assert f.getKey() == 7 and "7" in repr(f)
+    from pytorch_winoconv_b200 import WinoConv, dwm, dwm_convnd, matrix_conv, matrix_conv3d, matrix_convnd
+    for mod, names in [(dwm, ["dwm2d", "dwm3d", "dwm2d_", "dwm3d_"]),
+                       (matrix_conv, ["conv16", "conv32", "conv", "base_conv32", "matrix_alloc"]),
+                       (matrix_conv3d, ["conv16", "conv32", "conv", "base_conv32", "matrix_alloc"]),
+                       (matrix_convnd, ["conv32", "conv", "base_conv32", "matrix_alloc"]),
+                       (dwm_convnd, ["conv32"]), (WinoConv, ["Wino"])]:
+        for n in names:
+            assert hasattr(mod, n), (mod.__name__, n)
+    with pytest.raises(RuntimeError):
+        dwm.dwm2d(torch.zeros(1, 4, 8, 8), torch.zeros(4, 4, 3, 3))     # CPU tensors: no CPU path
