@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the Winograd / DWM forward-convolution path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload vgg16|cfg2]
+
+Workload (default): BASELINE config 5 -- the 13-convolution VGG-16 stack (3x3/s1/p1, ReLU, five
+2x2 max-pools), fp16, input 3x224x224 ~ U(0,1), Kaiming-normal weights, batch 256 per GPU
+(synthetic data, random weights; every rank holds its own shard, no collective on the data path).
+A step is one pass of the stack over the rank's batch.  One JSON line is printed by rank 0:
+
+  value      images/s of the whole job with the batch resident in HBM (CUDA-graph replay of the stack,
+             CUDA events, max over ranks)
+  e2e        the same through the public API from pinned host memory: H2D copy of the batch, the
+             stack, D2H copy of the result, every step
+  layers     per-layer device time, effective direct-conv TFLOP/s and fraction of the layer's roofline
+             t_roof = max(F_gemm / TC_peak, B_alg / HBM_peak)
+  roofline   the kernel class with the largest share of device time, measured with CUDA events around
+             every launch of an instrumented pass (winoconv_forward_timed)
+  cpu_baseline  the reference's torch-level Winograd algebra (oracle restatement) timed on this host's
+             cores on a bounded sample of the same workload
+
+`--impl reference` times that CPU restatement alone (the reference's own Python modules need the
+reference checkout, which does not travel to the GPU box, and its CUDA path has no 2-D 3x3 entry).
+With N > 1 this file is launched by torchrun (one rank per GPU); run directly with --gpus N it
+re-launches itself that way.
+"""
+import argparse
+import json
+import os
+import socket
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
+# summarised under profiles/ (None until a capture exists for that kernel and workload).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg2"])
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: 256 for vgg16, 32 for cfg2)")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the cpu_baseline sample")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks: sample nvidia-smi while the timed regions run
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.path = os.path.join(ROOT, "gpurun_out", f"bench_clocks_{gpu_index}.csv")
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            os.makedirs(os.path.dirname(self.path), exist_ok=True)
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=self.fh, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "power_w_max": max(power), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# the CPU arm (cpu_baseline and --impl reference)
+# ---------------------------------------------------------------------------------------------------
+def vgg_weights(dtype, seed=100):
+    from oracle import winograd_oracle as wo
+    return [wo.kaiming_normal((k, c, 3, 3), seed + i).to(dtype) for i, (c, k) in enumerate(wo.VGG16_CHANNELS)]
+
+
+def cpu_vgg_images_per_s(seconds_budget, chunk=2):
+    """Reference-style fp32 F(2x2,3x3) Winograd on the host cores over a bounded sample of the workload."""
+    import torch
+    from oracle import winograd_oracle as wo
+    torch.set_num_threads(os.cpu_count() or 1)
+    ws = vgg_weights(torch.float32)
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(chunk, 3, 224, 224, generator=g)
+    wo.vgg16_winograd_cpu(x[:1], ws)                     # warm-up (thread pools, allocator)
+    images, t0 = 0, time.perf_counter()
+    while True:
+        wo.vgg16_winograd_cpu(x, ws)
+        images += chunk
+        el = time.perf_counter() - t0
+        if el >= seconds_budget or images >= 256:
+            break
+    return images / el, images, el, torch.get_num_threads()
+
+
+def cpu_cfg2_layers_per_s(seconds_budget):
+    import torch
+    from oracle import winograd_oracle as wo
+    torch.set_num_threads(os.cpu_count() or 1)
+    x = torch.randn(32, 256, 28, 28, generator=torch.Generator().manual_seed(0))
+    w = wo.kaiming_normal((256, 256, 3, 3), 1)
+    wo.winograd_conv_cpu(x[:2], w, padding=1)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        wo.winograd_conv_cpu(x, w, padding=1, tile_m=2)
+        n += 1
+        el = time.perf_counter() - t0
+        if el >= seconds_budget:
+            break
+    return n / el, n, el, torch.get_num_threads()
+
+
+def run_reference(args):
+    """The reference arm: its torch-level Winograd path (CPU restatement) on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle import winograd_oracle as wo
+    torch.set_num_threads(os.cpu_count() or 1)
+    chunk = 2
+    if args.workload == "vgg16":
+        ws = vgg_weights(torch.float32)
+        x = torch.rand(chunk, 3, 224, 224, generator=torch.Generator().manual_seed(0))
+        step = lambda: wo.vgg16_winograd_cpu(x, ws)
+        units, metric, unit = chunk, "vgg16_conv_images_per_s", "images/s"
+        workload = "vgg16_conv_stack_3x224x224 (BASELINE configs[4])"
+        sample = f"{chunk} images per step, fp32 F(2x2,3x3), CPU"
+    else:
+        x = torch.randn(32, 256, 28, 28, generator=torch.Generator().manual_seed(0))
+        w = wo.kaiming_normal((256, 256, 3, 3), 1)
+        step = lambda: wo.winograd_conv_cpu(x, w, padding=1, tile_m=2)
+        units, metric, unit = 32, "conv_images_per_s", "images/s"
+        workload = "conv3x3_n32_c256_k256_28x28 (BASELINE configs[1])"
+        sample = "the full layer per step, fp32 F(2x2,3x3), CPU"
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    el = time.perf_counter() - t0
+    value = units * args.steps / el
+    cores = torch.get_num_threads()
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload, "device": "host CPU", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------
+def relaunch_under_torchrun(args):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
+    sys.exit(subprocess.call(cmd))
+
+
+def run_ours(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world == 1:
+        relaunch_under_torchrun(args)
+    import torch
+    import torch.distributed as dist
+    from pytorch_winoconv_b200 import capi, engine, sharding
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a B200: the engine has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    capi.check(capi.lib().winoconv_device_check(), "winoconv_device_check")
+    peaks, peaks_kind = load_peaks()
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+
+    # ---- build the workload ------------------------------------------------------------------
+    g = torch.Generator().manual_seed(1234 + rank)
+    if args.workload == "vgg16":
+        batch = args.batch or 256
+        ws = [w.to(dev) for w in vgg_weights(torch.float16)]
+        model = engine.VGG16ConvStack(ws, batch)
+        x_host = torch.rand(batch, 224, 224, 3, generator=g).half().pin_memory()
+        layers = model.layers
+        workload = "vgg16_conv_stack_3x224x224 (BASELINE configs[4])"
+        metric = "vgg16_conv_images_per_s"
+    else:
+        from oracle import winograd_oracle as wo   # Kaiming-normal helper only; nothing timed runs in the oracle
+        batch = args.batch or 32
+        w = wo.kaiming_normal((256, 256, 3, 3), 1).half().to(dev)
+        conv = engine.WinoConv((batch, 28, 28, 256), w, padding=1, tile_m=4)
+        out_buf = torch.empty(conv.out_shape, dtype=torch.float16, device=dev)
+
+        class _Single:
+            layers = [conv]
+            out_shape = conv.out_shape
+            launches_per_call = conv.launches_per_call
+            direct_flops = conv.info.direct_flops
+            _graph = None
+
+            def forward(self, x):
+                return conv(x, out=out_buf)
+
+            __call__ = forward
+            capture = engine.VGG16ConvStack.capture
+            replay = engine.VGG16ConvStack.replay
+            acts = [out_buf]
+
+        model = _Single()
+        x_host = torch.randn(batch, 28, 28, 256, generator=g).half().pin_memory()
+        layers = model.layers
+        workload = "conv3x3_n32_c256_k256_28x28_f43 (BASELINE configs[1])"
+        metric = "conv_images_per_s"
+    x_dev = x_host.to(dev, non_blocking=True)
+    y_host = torch.empty(model.out_shape, dtype=torch.float16).pin_memory()
+    torch.cuda.synchronize(dev)
+
+    use_graph = not args.no_graph
+    if use_graph:
+        model.capture(x_dev)
+        step = lambda: model.replay()
+    else:
+        step = lambda: model(x_dev)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # ---- region 1: inputs resident in HBM ---------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_local = e0.elapsed_time(e1)
+    ms = sharding.max_over_ranks(ms_local)
+    total_images = sharding.sum_over_ranks(batch)
+    value = total_images * args.steps / (ms / 1e3)
+
+    # ---- region 2: end to end from pinned host memory ---------------------------------------------
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y = model.replay(x_dev) if use_graph else model(x_dev)
+        y_host.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    ms_e2e = sharding.max_over_ranks(f0.elapsed_time(f1))
+    e2e_value = total_images * args.steps / (ms_e2e / 1e3)
+    clocks = sampler.stop()
+
+    # ---- instrumented pass: CUDA events around every launch ---------------------------------------
+    reps = 3
+    stage_names = ["input_transform", "gemm", "output_transform"]
+    per_layer = []
+    h = x_dev
+    for li, conv in enumerate(layers):
+        acc = [0.0, 0.0, 0.0]
+        n_launch = 0
+        conv.timed(h)                                    # warm
+        for _ in range(reps):
+            out, st, n_launch = conv.timed(h)
+            acc = [a + s for a, s in zip(acc, st)]
+        st = [a / reps for a in acc]
+        info = conv.info
+        t_ms = sum(st)
+        t_tc = info.gemm_flops / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
+        t_hbm = info.algorithmic_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+        per_layer.append({"layer": li + 1, "c": int(conv.desc.c_in), "k": int(conv.desc.k_out),
+                          "hw": int(conv.in_shape[1]), "ms": round(t_ms, 4), "stage_ms": [round(v, 4) for v in st],
+                          "launches": n_launch,
+                          "eff_tflops": round(info.direct_flops / (t_ms * 1e-3) / 1e12, 2),
+                          "gemm_tflops": round(info.gemm_flops / (st[1] * 1e-3) / 1e12, 2),
+                          "roof_ms": round(max(t_tc, t_hbm), 4), "roof_bound": "tensor" if t_tc >= t_hbm else "hbm",
+                          "roof_frac": round(max(t_tc, t_hbm) / t_ms, 4)})
+        h = out
+    stage_tot = [sum(l["stage_ms"][i] for l in per_layer) for i in range(3)]
+    dom = max(range(3), key=lambda i: stage_tot[i])
+    n_dom_launch = sum(l["launches"] // 3 for l in per_layer)
+    esz = 2
+    if dom == 1:
+        alg = sum(c.info.gemm_flops for c in layers)
+        achieved = alg / (stage_tot[1] * 1e-3) / 1e12
+        peak, unit, bound = peaks["bf16_tflops_sustained"], "TFLOP/s", "tensor"
+        kernel = "gemm_tcgen05_kernel"
+    else:
+        if dom == 0:   # algorithmic bytes of the input transform: it must read x once
+            alg = sum(float(esz) * c.desc.batch * c.in_shape[1] * c.in_shape[2] * c.desc.c_in for c in layers)
+            kernel = "input_transform_kernel"
+        else:          # the output transform must write y once
+            alg = sum(float(esz) * c.out_shape[0] * c.out_shape[1] * c.out_shape[2] * c.out_shape[3] for c in layers)
+            kernel = "output_transform_kernel"
+        achieved = alg / (stage_tot[dom] * 1e-3) / 1e9
+        peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
+    roofline = {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": unit,
+                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, kernel)),
+                "kernel": kernel, "launches_per_step": n_dom_launch,
+                "avg_launch_us": round(1e3 * stage_tot[dom] / max(n_dom_launch, 1), 2),
+                "peak_source": f"MEASURED_PEAKS.json ({peaks_kind}; sustained bf16 figure, copy bandwidth)",
+                "stage_share": {n: round(t / sum(stage_tot), 4) for n, t in zip(stage_names, stage_tot)}}
+    step_roof_ms = sum(l["roof_ms"] for l in per_layer)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        if args.workload == "vgg16":
+            v, n, el, cores = cpu_vgg_images_per_s(args.cpu_seconds)
+            cpu_baseline = {"value": round(v, 3), "unit": "images/s", "cores": cores, "kind": "port",
+                            "sample": f"{n} images of the same stack in {el:.1f} s, fp32 F(2x2,3x3) tile algebra "
+                                      "(reference torch-level path restated in oracle/)"}
+        else:
+            v, n, el, cores = cpu_cfg2_layers_per_s(args.cpu_seconds)
+            cpu_baseline = {"value": round(v * 32, 3), "unit": "images/s", "cores": cores, "kind": "port",
+                            "sample": f"{n} passes of the same layer in {el:.1f} s, fp32 F(2x2,3x3), CPU"}
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    flops_per_image = model.direct_flops / batch
+    line = {
+        "metric": metric, "value": round(value, 2), "unit": "images/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": workload, "per_gpu_batch": batch, "global_batch": int(total_images),
+                   "parallelism": f"batch shards x{world}, no collective", "launch": "cuda_graph" if use_graph else "eager",
+                   "l2": "activations and scratch of every step exceed the 126 MB L2 (inputs larger than L2)",
+                   "weights": "filter transforms precomputed outside the timed region",
+                   "accumulate": "fp32", "winograd": "F(4x4,3x3), products fp32"},
+        "effective_tflops": round(value * flops_per_image / 1e12, 2),
+        "step_roofline_frac": round(step_roof_ms / (ms / args.steps), 4),
+        "e2e": {"value": round(e2e_value, 2), "unit": "images/s", "ms_per_step": round(ms_e2e / args.steps, 4),
+                "h2d_bytes_per_step": int(x_host.numel() * x_host.element_size() * world),
+                "d2h_bytes_per_step": int(y_host.numel() * y_host.element_size() * world)},
+        "gpu_launches": int(model.launches_per_call * args.steps),
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": clocks, "layers": per_layer,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

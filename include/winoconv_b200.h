@@ -147,6 +147,16 @@ WINOCONV_API int winoconv_forward(const winoconv_desc_t *desc, const void *x, co
                      void *v_ws, size_t v_ws_bytes, void *m_ws, size_t m_ws_bytes, void *stream);
 
 /*
+ * winoconv_forward with CUDA events around its three stages.  Synchronises the stream, then
+ * writes the summed device time of the input transforms, GEMMs and output transforms (ms) to
+ * stage_ms[0..2] and the number of kernels launched to *launches (may be NULL).
+ * The counterpart of the per-stage perf_counter prints inside dwm3d_ (dwm.py:44-107).
+ */
+WINOCONV_API int winoconv_forward_timed(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias,
+                                        void *y, void *v_ws, size_t v_ws_bytes, void *m_ws, size_t m_ws_bytes,
+                                        void *stream, float *stage_ms, int32_t *launches);
+
+/*
  * The per-position batched GEMM on its own: m[p][t][k] = sum_c v[p][t][c] * u[p][k][c],
  * fp32 accumulate.  v [positions][tiles][c_pad], u [positions][k_out][c_pad] in `dtype`,
  * m [positions][tiles][k_out] in `product_dtype`.  c_pad must be a multiple of 8.

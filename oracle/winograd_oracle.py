@@ -285,3 +285,16 @@ def vgg16_conv_stack_f64(x: torch.Tensor, weights: Sequence[torch.Tensor], round
         if round_to is not None:
             h = h.to(round_to).double()
     return h
+
+
+def vgg16_winograd_cpu(x: torch.Tensor, weights: Sequence[torch.Tensor], tile_m: int = 2) -> torch.Tensor:
+    """The VGG-16 conv stack evaluated the reference's way on CPU: every 3x3 convolution through
+    pad -> tile split -> F(tile_m,3) algebra in fp32 -> concat (matrix_conv.py:92-135 ->
+    matrix_convnd.py:110-153), then ReLU and the max-pools in torch.  This is the timed CPU
+    baseline; fp16 shapes are run in fp32 here, as a CPU has no half GEMM worth timing."""
+    h = x.detach().cpu().float()
+    for i, wt in enumerate(weights):
+        h = F.relu(winograd_conv_cpu(h, wt, padding=1, tile_m=tile_m))
+        if i in VGG16_POOL_AFTER:
+            h = F.max_pool2d(h, 2)
+    return h

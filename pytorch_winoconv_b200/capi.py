@@ -25,7 +25,7 @@ MAX_PIECES = 64
 EXPORTED_SYMBOLS = (
     "winoconv_abi_version", "winoconv_status_string", "winoconv_last_error", "winoconv_device_check",
     "winoconv_plan", "winoconv_plan_pieces", "winoconv_filter_transform", "winoconv_forward",
-    "winoconv_gemm_batched", "winoconv_split", "winoconv_concat", "winoconv_add",
+    "winoconv_forward_timed", "winoconv_gemm_batched", "winoconv_split", "winoconv_concat", "winoconv_add",
     "winoconv_read_device_error",
 )
 
@@ -75,6 +75,8 @@ def lib() -> ctypes.CDLL:
     L.winoconv_filter_transform.argtypes = [POINTER(Desc), c_void_p, c_void_p, c_void_p]
     L.winoconv_forward.argtypes = [POINTER(Desc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                    c_void_p, c_size_t, c_void_p]
+    L.winoconv_forward_timed.argtypes = [POINTER(Desc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                         c_void_p, c_size_t, c_void_p, POINTER(ctypes.c_float), POINTER(c_int32)]
     L.winoconv_gemm_batched.argtypes = [c_int, c_int, c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p,
                                         c_void_p, c_void_p]
     L.winoconv_split.argtypes = [c_void_p, c_void_p] + [c_int] * 14 + [c_void_p]
@@ -82,7 +84,7 @@ def lib() -> ctypes.CDLL:
     L.winoconv_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     L.winoconv_read_device_error.argtypes = [c_void_p, POINTER(c_uint32)]
     for name in ("winoconv_plan", "winoconv_plan_pieces", "winoconv_filter_transform", "winoconv_forward",
-                 "winoconv_gemm_batched", "winoconv_split", "winoconv_concat", "winoconv_add",
+                 "winoconv_forward_timed", "winoconv_gemm_batched", "winoconv_split", "winoconv_concat", "winoconv_add",
                  "winoconv_read_device_error"):
         getattr(L, name).restype = c_int
     _lib = L
@@ -143,6 +145,16 @@ def forward(desc: Desc, x_ptr: int, u_ptr: int, bias_ptr, y_ptr: int, v_ptr: int
             m_bytes: int, stream: int = 0) -> None:
     check(lib().winoconv_forward(byref(desc), x_ptr, u_ptr, bias_ptr, y_ptr, v_ptr, v_bytes, m_ptr, m_bytes, stream),
           "winoconv_forward")
+
+
+def forward_timed(desc: Desc, x_ptr: int, u_ptr: int, bias_ptr, y_ptr: int, v_ptr: int, v_bytes: int, m_ptr: int,
+                  m_bytes: int, stream: int = 0):
+    """Returns ([input_transform_ms, gemm_ms, output_transform_ms], kernels_launched)."""
+    ms = (ctypes.c_float * 3)()
+    n = c_int32(0)
+    check(lib().winoconv_forward_timed(byref(desc), x_ptr, u_ptr, bias_ptr, y_ptr, v_ptr, v_bytes, m_ptr, m_bytes,
+                                       stream, ms, byref(n)), "winoconv_forward_timed")
+    return [float(v) for v in ms], int(n.value)
 
 
 def gemm_batched(dtype, product_dtype, engine, positions, tiles, c_pad, k_out, v_ptr, u_ptr, m_ptr, stream=0) -> None:

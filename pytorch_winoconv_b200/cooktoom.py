@@ -37,6 +37,11 @@ _LONG_POINTS = (0, 1, -1, Fraction(1, 2), -Fraction(1, 2), Fraction(1, 3), -Frac
                 Fraction(3, 2), -Fraction(3, 2), -3, 2, -2)
 
 
+# Points of the engine's F(4,3) device code (wino_common.cuh, Xf<4,3>): symmetric and dyadic,
+# chosen for low fp16 error (see the comment there).
+ENGINE_F43_POINTS = (Fraction(0), Fraction(5, 8), -Fraction(5, 8), Fraction(3, 2), -Fraction(3, 2))
+
+
 def default_points(m: int, r: int) -> Tuple[Fraction, ...]:
     alpha = m + r - 1
     need = alpha - 1

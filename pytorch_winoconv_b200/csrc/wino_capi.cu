@@ -271,8 +271,9 @@ int winoconv_filter_transform(const winoconv_desc_t *desc, const void *weights, 
   return WINOCONV_OK;
 }
 
-int winoconv_forward(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias, void *y, void *v_ws,
-                     size_t v_ws_bytes, void *m_ws, size_t m_ws_bytes, void *stream) {
+static int forward_impl(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias, void *y,
+                        void *v_ws, size_t v_ws_bytes, void *m_ws, size_t m_ws_bytes, void *stream, float *stage_ms,
+                        int32_t *launches) {
   Plan plan;
   int st = build_plan(desc, &plan);
   if (st != WINOCONV_OK) return st;
@@ -291,16 +292,59 @@ int winoconv_forward(const winoconv_desc_t *desc, const void *x, const void *u, 
                                             std::to_string(std::min<long long>(128, g.T)) + " (see winoconv_plan)");
   if (block < g.T) block = block / 128 * 128;
   cudaStream_t s = (cudaStream_t)stream;
-  for (long long t0 = 0; t0 < g.T; t0 += block) {
+  std::vector<cudaEvent_t> ev;  // four events per pass when stage times are wanted
+  auto mark = [&]() -> cudaError_t {
+    if (!stage_ms) return cudaSuccess;
+    cudaEvent_t e;
+    cudaError_t r = cudaEventCreate(&e);
+    if (r != cudaSuccess) return r;
+    ev.push_back(e);
+    return cudaEventRecord(e, s);
+  };
+  int n_launch = 0;
+  int result = WINOCONV_OK;
+  for (long long t0 = 0; t0 < g.T && result == WINOCONV_OK; t0 += block) {
     const int n = (int)std::min<long long>(block, g.T - t0);
-    cudaError_t e = launch_input_transform(g, plan.dtype, x, v_ws, t0, n, s);
-    if (e != cudaSuccess) return cuda_fail(e, "input transform launch");
-    st = run_gemm(plan.dtype, plan.product_dtype, plan.engine, g.positions, n, g.Cp, g.K, v_ws, u, m_ws, s);
-    if (st != WINOCONV_OK) return st;
+    cudaError_t e = mark();
+    if (e == cudaSuccess) e = launch_input_transform(g, plan.dtype, x, v_ws, t0, n, s);
+    if (e != cudaSuccess) { result = cuda_fail(e, "input transform launch"); break; }
+    if ((e = mark()) != cudaSuccess) { result = cuda_fail(e, "event record"); break; }
+    result = run_gemm(plan.dtype, plan.product_dtype, plan.engine, g.positions, n, g.Cp, g.K, v_ws, u, m_ws, s);
+    if (result != WINOCONV_OK) break;
+    if ((e = mark()) != cudaSuccess) { result = cuda_fail(e, "event record"); break; }
     e = launch_output_transform(g, plan.dtype, plan.product_dtype, m_ws, y, bias, t0, n, s);
-    if (e != cudaSuccess) return cuda_fail(e, "output transform launch");
+    if (e != cudaSuccess) { result = cuda_fail(e, "output transform launch"); break; }
+    if ((e = mark()) != cudaSuccess) { result = cuda_fail(e, "event record"); break; }
+    n_launch += 3;
   }
-  return WINOCONV_OK;
+  if (launches) *launches = n_launch;
+  if (stage_ms) {
+    stage_ms[0] = stage_ms[1] = stage_ms[2] = 0.f;
+    if (result == WINOCONV_OK) {
+      cudaError_t e = cudaStreamSynchronize(s);
+      if (e != cudaSuccess) result = cuda_fail(e, "stream synchronize");
+      for (size_t i = 0; result == WINOCONV_OK && i + 3 < ev.size(); i += 4)
+        for (int j = 0; j < 3; ++j) {
+          float ms = 0.f;
+          if ((e = cudaEventElapsedTime(&ms, ev[i + j], ev[i + j + 1])) != cudaSuccess) { result = cuda_fail(e, "event elapsed"); break; }
+          stage_ms[j] += ms;
+        }
+    }
+    for (cudaEvent_t e : ev) cudaEventDestroy(e);
+  }
+  return result;
+}
+
+int winoconv_forward(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias, void *y, void *v_ws,
+                     size_t v_ws_bytes, void *m_ws, size_t m_ws_bytes, void *stream) {
+  return forward_impl(desc, x, u, bias, y, v_ws, v_ws_bytes, m_ws, m_ws_bytes, stream, nullptr, nullptr);
+}
+
+int winoconv_forward_timed(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias, void *y,
+                           void *v_ws, size_t v_ws_bytes, void *m_ws, size_t m_ws_bytes, void *stream,
+                           float *stage_ms, int32_t *launches) {
+  if (!stage_ms) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null stage_ms");
+  return forward_impl(desc, x, u, bias, y, v_ws, v_ws_bytes, m_ws, m_ws_bytes, stream, stage_ms, launches);
 }
 
 int winoconv_gemm_batched(int dtype, int product_dtype, int gemm_engine, int positions, int64_t tiles, int c_pad,

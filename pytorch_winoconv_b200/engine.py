@@ -113,6 +113,17 @@ class WinoConv:
                          out.data_ptr(), v.data_ptr(), v.numel(), m.data_ptr(), m.numel(), _stream_ptr(self.device))
         return out
 
+    def timed(self, x: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """Forward with CUDA events around the three stages: (y, [ms_in, ms_gemm, ms_out], launches)."""
+        if out is None:
+            out = torch.empty(self.out_shape, dtype=self.dtype, device=self.device)
+        v, m = self.pool.get(self.device, int(self.info.input_ws_bytes), int(self.info.product_ws_bytes))
+        with torch.cuda.device(self.device):
+            ms, n = capi.forward_timed(self.desc, x.data_ptr(), self.u.data_ptr(),
+                                       None if self.bias is None else self.bias.data_ptr(), out.data_ptr(),
+                                       v.data_ptr(), v.numel(), m.data_ptr(), m.numel(), _stream_ptr(self.device))
+        return out, ms, n
+
     @property
     def launches_per_call(self) -> int:
         """Kernels this forward launches: three per pass over a block of tiles."""

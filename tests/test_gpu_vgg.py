@@ -1,0 +1,46 @@
+"""VGG-16 convolution stack (BASELINE config 5) on the device against the float64 stack."""
+import pytest
+import torch
+
+from oracle import winograd_oracle as wo
+from pytorch_winoconv_b200 import capi, engine
+
+pytestmark = pytest.mark.gpu
+
+
+def _weights(dtype):
+    return [wo.kaiming_normal((k, c, 3, 3), 100 + i).to(dtype) for i, (c, k) in enumerate(wo.VGG16_CHANNELS)]
+
+
+def test_vgg16_stack_matches_float64_stack():
+    batch = 2
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(batch, 3, 224, 224, generator=g).half()
+    ws = _weights(torch.float16)
+    stack = engine.VGG16ConvStack([w.cuda() for w in ws], batch)
+    xl = x.permute(0, 2, 3, 1).contiguous().cuda()
+    y = stack(xl).permute(0, 3, 1, 2).float().cpu()
+    torch.cuda.synchronize()
+    assert capi.read_device_error() == 0
+    assert tuple(y.shape) == (batch, 512, 7, 7)
+    # errors compound over 13 layers; compare with the float64 stack fed the same fp16 inputs
+    o = wo.vgg16_conv_stack_f64(x, ws)
+    err = wo.error_metrics(y, o)
+    print("vgg16 stack error vs float64", err)
+    assert err["E_A"] < 3e-2, err
+    # per-layer check: layer i of the engine against float64 on the engine's own layer input
+    h = xl
+    for i, conv in enumerate(stack.layers):
+        out = conv(h)
+        hin = h.permute(0, 3, 1, 2).cpu()
+        ref = torch.relu(wo.direct_conv_f64(hin, ws[i], padding=1))
+        if i in wo.VGG16_POOL_AFTER:
+            ref = torch.nn.functional.max_pool2d(ref, 2)
+        e = wo.error_metrics(out.permute(0, 3, 1, 2).cpu(), ref)
+        assert e["E_A"] < 1e-2, (i, e)
+        h = out.clone()
+    # CUDA-graph replay gives the same bits as eager
+    stack.capture(xl)
+    yg = stack.replay(xl).permute(0, 3, 1, 2).float().cpu()
+    assert torch.equal(yg, y)
+    assert stack.launches_per_call >= 39
