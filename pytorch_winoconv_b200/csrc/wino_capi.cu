@@ -46,11 +46,10 @@ struct Plan {
 // Working set the forward aims for (V block + M block), in bytes: small enough to stay in the 126 MB L2
 // between the three kernels of a pass.  A layer whose whole V + M fits kWholeBytesLimit runs as one pass.
 // WINOCONV_BLOCK_MB / WINOCONV_WHOLE_MB override them (read once) for tuning.
-unsigned long long env_mb(const char *name, unsigned long long dflt) {
+unsigned long long env_mb(const char *name, unsigned long long dflt_mb) {
   const char *v = getenv(name);
-  if (!v || !*v) return dflt;
-  const long long mb = atoll(v);
-  return mb > 0 ? (unsigned long long)mb << 20 : dflt;
+  const long long mb = (v && *v) ? atoll(v) : 0;
+  return (mb > 0 ? (unsigned long long)mb : dflt_mb) << 20;
 }
 unsigned long long block_bytes_target() { static const unsigned long long v = env_mb("WINOCONV_BLOCK_MB", 48); return v; }
 unsigned long long whole_bytes_limit() { static const unsigned long long v = env_mb("WINOCONV_WHOLE_MB", 96); return v; }
