@@ -157,6 +157,28 @@ WINOCONV_API int winoconv_forward_timed(const winoconv_desc_t *desc, const void 
                                         void *stream, float *stage_ms, int32_t *launches);
 
 /*
+ * winoconv_forward for callers that may not allocate device memory at all -- a plugin inside a host
+ * application that has handed the whole device to its own memory pool, or a latency-critical loop that
+ * cannot afford the device-wide stall of cudaMalloc.  The caller passes only inputs and outputs; the V and
+ * M scratch of the pass live in a WINOCONV_STATIC_SCRATCH_BYTES array that is part of the library image, so
+ * every GPU that loads the library holds those 32 MiB until the process exits.  Nothing here calls
+ * cudaMalloc, cudaFree or any allocating library routine.
+ *   - Limit: 128 tiles of scratch (winoconv_plan: input_ws_bytes_min + product_ws_bytes_min) must fit the
+ *     array; larger layers are refused with WINOCONV_ERR_WORKSPACE and a message stating both sizes.
+ *     Layers that fit are walked in as many passes as the array allows.
+ *   - The first call on each device looks up the array's device address (with that device current) and
+ *     keeps it; make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left.  Nothing
+ *     needs clearing: every scratch element a pass reads was written earlier in the same pass.  Two calls
+ *     whose kernels can overlap on the GPU (different streams, no dependency) race on the array -- order them.
+ * No counterpart in the reference, whose launcher allocates and frees on every call
+ * (src/base_conv_launchers.cu:323-336,376,384-391).
+ */
+#define WINOCONV_STATIC_SCRATCH_BYTES (32u << 20)
+WINOCONV_API int winoconv_forward_static(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias,
+                                         void *y, void *stream);
+
+/*
  * The per-position batched GEMM on its own: m[p][t][k] = sum_c v[p][t][c] * u[p][k][c],
  * fp32 accumulate.  v [positions][tiles][c_pad], u [positions][k_out][c_pad] in `dtype`,
  * m [positions][tiles][k_out] in `product_dtype`.  c_pad must be a multiple of 8.

@@ -25,8 +25,8 @@ MAX_PIECES = 64
 EXPORTED_SYMBOLS = (
     "winoconv_abi_version", "winoconv_status_string", "winoconv_last_error", "winoconv_device_check",
     "winoconv_plan", "winoconv_plan_pieces", "winoconv_filter_transform", "winoconv_forward",
-    "winoconv_forward_timed", "winoconv_gemm_batched", "winoconv_split", "winoconv_concat", "winoconv_add",
-    "winoconv_read_device_error",
+    "winoconv_forward_timed", "winoconv_forward_static", "winoconv_gemm_batched", "winoconv_split",
+    "winoconv_concat", "winoconv_add", "winoconv_read_device_error",
 )
 
 
@@ -77,6 +77,7 @@ def lib() -> ctypes.CDLL:
                                    c_void_p, c_size_t, c_void_p]
     L.winoconv_forward_timed.argtypes = [POINTER(Desc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                          c_void_p, c_size_t, c_void_p, POINTER(ctypes.c_float), POINTER(c_int32)]
+    L.winoconv_forward_static.argtypes = [POINTER(Desc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     L.winoconv_gemm_batched.argtypes = [c_int, c_int, c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p,
                                         c_void_p, c_void_p]
     L.winoconv_split.argtypes = [c_void_p, c_void_p] + [c_int] * 14 + [c_void_p]
@@ -84,8 +85,8 @@ def lib() -> ctypes.CDLL:
     L.winoconv_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     L.winoconv_read_device_error.argtypes = [c_void_p, POINTER(c_uint32)]
     for name in ("winoconv_plan", "winoconv_plan_pieces", "winoconv_filter_transform", "winoconv_forward",
-                 "winoconv_forward_timed", "winoconv_gemm_batched", "winoconv_split", "winoconv_concat", "winoconv_add",
-                 "winoconv_read_device_error"):
+                 "winoconv_forward_timed", "winoconv_forward_static", "winoconv_gemm_batched", "winoconv_split",
+                 "winoconv_concat", "winoconv_add", "winoconv_read_device_error"):
         getattr(L, name).restype = c_int
     _lib = L
     return L
@@ -145,6 +146,15 @@ def forward(desc: Desc, x_ptr: int, u_ptr: int, bias_ptr, y_ptr: int, v_ptr: int
             m_bytes: int, stream: int = 0) -> None:
     check(lib().winoconv_forward(byref(desc), x_ptr, u_ptr, bias_ptr, y_ptr, v_ptr, v_bytes, m_ptr, m_bytes, stream),
           "winoconv_forward")
+
+
+STATIC_SCRATCH_BYTES = 32 << 20
+
+
+def forward_static(desc: Desc, x_ptr: int, u_ptr: int, bias_ptr, y_ptr: int, stream: int = 0) -> None:
+    """winoconv_forward_static: the forward with the library's built-in 32 MiB scratch array -- for callers
+    that may not allocate device memory.  Calls on one device share that array, so they must not overlap."""
+    check(lib().winoconv_forward_static(byref(desc), x_ptr, u_ptr, bias_ptr, y_ptr, stream), "winoconv_forward_static")
 
 
 def forward_timed(desc: Desc, x_ptr: int, u_ptr: int, bias_ptr, y_ptr: int, v_ptr: int, v_bytes: int, m_ptr: int,

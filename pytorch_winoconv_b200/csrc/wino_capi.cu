@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -344,6 +345,53 @@ int winoconv_forward_timed(const winoconv_desc_t *desc, const void *x, const voi
                            float *stage_ms, int32_t *launches) {
   if (!stage_ms) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null stage_ms");
   return forward_impl(desc, x, u, bias, y, v_ws, v_ws_bytes, m_ws, m_ws_bytes, stream, stage_ms, launches);
+}
+
+// ---- scratch that is part of the library image (winoconv_forward_static) ---------------------------------
+// In host code the name below is only a handle for cudaGetSymbolAddress; the address kernels may use is
+// looked up once per device and kept in g_static_scratch_addr.
+static __device__ __align__(256) unsigned char g_static_scratch[WINOCONV_STATIC_SCRATCH_BYTES];
+static void *g_static_scratch_addr[64] = {};
+static std::mutex g_static_scratch_mu;
+
+static int static_scratch_of_current_device(unsigned char **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(WINOCONV_ERR_UNSUPPORTED, "device ordinal beyond 63");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+  if (!g_static_scratch_addr[dev]) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = static_cast<unsigned char *>(g_static_scratch_addr[dev]);
+  return WINOCONV_OK;
+}
+
+int winoconv_forward_static(const winoconv_desc_t *desc, const void *x, const void *u, const void *bias, void *y,
+                            void *stream) {
+  Plan plan;
+  int st = build_plan(desc, &plan);
+  if (st != WINOCONV_OK) return st;
+  if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
+  const winoconv_plan_info_t &I = plan.info;
+  const unsigned long long tiles_min = (unsigned long long)std::min<long long>(128, I.tiles);
+  const unsigned long long v_tile = I.input_ws_bytes_min / tiles_min, m_tile = I.product_ws_bytes_min / tiles_min;
+  const unsigned long long usable = WINOCONV_STATIC_SCRATCH_BYTES - 256;  // V is rounded up to the M alignment
+  if (tiles_min * (v_tile + m_tile) > usable)
+    return fail(WINOCONV_ERR_WORKSPACE, "this layer needs " + std::to_string(tiles_min * (v_tile + m_tile)) +
+                                            " bytes of scratch for its smallest pass; the built-in array holds " +
+                                            std::to_string(WINOCONV_STATIC_SCRATCH_BYTES) +
+                                            " (use winoconv_forward with caller scratch)");
+  unsigned long long block = std::min<unsigned long long>(usable / (v_tile + m_tile), (unsigned long long)I.tiles);
+  if (block < (unsigned long long)I.tiles) block = block / 128 * 128;
+  const size_t v_bytes = (size_t)((block * v_tile + 255) / 256 * 256);
+  unsigned char *base = nullptr;
+  if ((st = static_scratch_of_current_device(&base)) != WINOCONV_OK) return st;
+  return forward_impl(desc, x, u, bias, y, base, v_bytes, base + v_bytes, WINOCONV_STATIC_SCRATCH_BYTES - v_bytes, stream,
+                      nullptr, nullptr);
 }
 
 int winoconv_gemm_batched(int dtype, int product_dtype, int gemm_engine, int positions, int64_t tiles, int c_pad,

@@ -1,0 +1,54 @@
+"""winoconv_forward_static -- the forward for callers that may not allocate device memory -- against
+winoconv_forward on the same inputs.  The built-in scratch array is shared by all calls and keeps the
+previous call's contents, so the check runs two different layers back to back, then the first again.
+Collected last on purpose (file name), and self-contained so it also passes alone in a fresh process."""
+import pytest
+import torch
+
+from pytorch_winoconv_b200 import capi, engine
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float16: 2e-2, torch.float32: 1e-3}     # the E_B bounds of tests/gpu_util.py
+
+
+def _layer(seed, n, c, k, hw, ks, pad, dtype, tile_m=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, hw, hw, c, generator=g).to(dtype).cuda()
+    w = (torch.randn(k, c, ks, ks, generator=g) * (2.0 / (c * ks * ks)) ** 0.5).to(dtype).cuda()
+    conv = engine.WinoConv(x.shape, w, padding=pad, tile_m=tile_m)
+    return x, conv
+
+
+def _both(x, conv):
+    y_ref = conv(x).clone()                                    # existing entry point, caller scratch
+    y = torch.full_like(y_ref, float("nan"))
+    capi.forward_static(conv.desc, x.data_ptr(), conv.u.data_ptr(), None, y.data_ptr(),
+                        torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert capi.read_device_error() == 0
+    assert torch.isfinite(y).all()
+    d = (y.double() - y_ref.double()).abs()
+    rms = y_ref.double().pow(2).mean().sqrt()
+    e_b = (d / torch.maximum(y_ref.double().abs(), rms)).max().item()
+    assert e_b <= TOL[x.dtype], e_b
+    return e_b
+
+
+def test_static_scratch_forward_matches_on_consecutive_calls():
+    # layer A needs several passes through the 32 MiB array; layer B is a different shape and dtype
+    xa, ca = _layer(1, 16, 64, 96, 56, 3, 1, torch.float16)
+    xb, cb = _layer(2, 2, 24, 40, 21, 5, 2, torch.float32)
+    need_a = int(ca.info.tiles) * (int(ca.info.input_ws_bytes_min) + int(ca.info.product_ws_bytes_min)) // 128
+    assert need_a > capi.STATIC_SCRATCH_BYTES            # so the array is reused within one call
+    errs = [_both(xa, ca), _both(xb, cb), _both(xa, ca)]
+    print("forward_static vs forward, E_B:", errs)
+
+
+def test_static_scratch_refuses_oversized_layers():
+    # 3-D 3x3x3 with 1024 -> 1024 channels: 64 positions x (1024*2 + 1024*4) B x 128 tiles = 48 MiB > 32 MiB (512 tiles in all)
+    d = capi.make_desc(ndim=3, batch=1, c_in=1024, k_out=1024, in_size=(16, 16, 16), ker_size=3, pad=1)
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.forward_static(d, 256, 256, None, 256)
+    assert ei.value.status == capi.ERR_WORKSPACE
+    assert "33554432" in str(ei.value)
