@@ -62,6 +62,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg2"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: 256 for vgg16, 32 for cfg2)")
+    ap.add_argument("--algo", default="auto", choices=["auto", "row", "fused", "staged"],
+                    help="fused: one tcgen05 kernel per layer, F(2x2,3x3); staged: three kernels per pass, F(4x4,3x3)")
+    ap.add_argument("--product", default="f32", choices=["f32", "f16"], help="dtype of the staged algorithm's products M")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the cpu_baseline sample")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
@@ -245,7 +248,10 @@ def run_ours(args):
     if args.workload == "vgg16":
         batch = args.batch or 256
         ws = [w.to(dev) for w in vgg_weights(torch.float16)]
-        model = engine.VGG16ConvStack(ws, batch)
+        fused = args.algo in ("auto", "row", "fused")
+        algo_code = {"auto": capi.ALGO_ROW, "row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
+        model = engine.VGG16ConvStack(ws, batch, tile_m=2 if fused else 4, algo=algo_code,
+                                      product_dtype=torch.float16 if (args.product == "f16" and not fused) else None)
         x_host = torch.rand(batch, 224, 224, 3, generator=g).half().pin_memory()
         layers = model.layers
         workload = "vgg16_conv_stack_3x224x224 (BASELINE configs[4])"
@@ -254,7 +260,10 @@ def run_ours(args):
         from oracle import winograd_oracle as wo   # Kaiming-normal helper only; nothing timed runs in the oracle
         batch = args.batch or 32
         w = wo.kaiming_normal((256, 256, 3, 3), 1).half().to(dev)
-        conv = engine.WinoConv((batch, 28, 28, 256), w, padding=1, tile_m=4)
+        fused = args.algo in ("fused", "row")
+        algo_code = {"auto": capi.ALGO_STAGED, "row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
+        conv = engine.WinoConv((batch, 28, 28, 256), w, padding=1, tile_m=2 if fused else 4, algo=algo_code,
+                               product_dtype=torch.float16 if (args.product == "f16" and not fused) else None)
         out_buf = torch.empty(conv.out_shape, dtype=torch.float16, device=dev)
 
         class _Single:
@@ -352,13 +361,15 @@ def run_ours(args):
         h = out
     stage_tot = [sum(l["stage_ms"][i] for l in per_layer) for i in range(3)]
     dom = max(range(3), key=lambda i: stage_tot[i])
-    n_dom_launch = sum(l["launches"] // 3 for l in per_layer)
+    is_fused = all(c.info.algo in (capi.ALGO_FUSED, capi.ALGO_ROW) for c in layers)
+    is_row = all(c.info.algo == capi.ALGO_ROW for c in layers)
+    n_dom_launch = sum(l["launches"] if is_fused else l["launches"] // 3 for l in per_layer)
     esz = 2
     if dom == 1:
         alg = sum(c.info.gemm_flops for c in layers)
         achieved = alg / (stage_tot[1] * 1e-3) / 1e12
         peak, unit, bound = peaks["bf16_tflops_sustained"], "TFLOP/s", "tensor"
-        kernel = "gemm_tcgen05_kernel"
+        kernel = "rowfused_kernel" if is_row else ("fused23_kernel" if is_fused else "gemm_tcgen05_kernel")
     else:
         if dom == 0:   # algorithmic bytes of the input transform: it must read x once
             alg = sum(float(esz) * c.desc.batch * c.in_shape[1] * c.in_shape[2] * c.desc.c_in for c in layers)
@@ -402,7 +413,10 @@ def run_ours(args):
                    "parallelism": f"batch shards x{world}, no collective", "launch": "cuda_graph" if use_graph else "eager",
                    "l2": "activations and scratch of every step exceed the 126 MB L2 (inputs larger than L2)",
                    "weights": "filter transforms precomputed outside the timed region",
-                   "accumulate": "fp32", "winograd": "F(4x4,3x3), products fp32"},
+                   "accumulate": "fp32",
+                   "winograd": ("DWM 1x3 row pieces, F(2,3) along W, one fused tcgen05 kernel per layer" if is_row else
+                                "F(2x2,3x3) fused: gather + transforms + tcgen05 GEMM in one kernel per layer" if is_fused
+                                else "F(4x4,3x3) staged: input transform, tcgen05 GEMM, output transform; products fp32")},
         "effective_tflops": round(value * flops_per_image / 1e12, 2),
         "step_roofline_frac": round(step_roof_ms / (ms / args.steps), 4),
         "e2e": {"value": round(e2e_value, 2), "unit": "images/s", "ms_per_step": round(ms_e2e / args.steps, 4),

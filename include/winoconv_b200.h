@@ -52,6 +52,15 @@ typedef enum winoconv_gemm {
   WINOCONV_GEMM_TCGEN05 = 2  /* tcgen05.mma + TMEM + TMA (f16 / bf16 inputs only)         */
 } winoconv_gemm_t;
 
+typedef enum winoconv_algo {
+  WINOCONV_ALGO_AUTO = 0,   /* ROW where it applies, else FUSED where it applies, else STAGED            */
+  WINOCONV_ALGO_STAGED = 1, /* input transform -> batched GEMM -> output transform through V / M scratch  */
+  WINOCONV_ALGO_FUSED = 2,  /* one tcgen05 kernel, 3x3 pieces as F(2x2,3x3); f16 / bf16, any stride       */
+  WINOCONV_ALGO_ROW = 3     /* one tcgen05 kernel, 1x3 pieces: F(2,3) along W, taps along H / depth summed */
+                            /* in TMEM; f16 / bf16, stride 1, kernel <= 7 taps tall.  Scratch only to pad  */
+                            /* the channels of x to a multiple of 8 (v_ws, winoconv_plan: input_ws_bytes)  */
+} winoconv_algo_t;
+
 /* epilogue bits, applied inside the output transform */
 #define WINOCONV_EPI_BIAS 1u  /* y += bias[k]                                  */
 #define WINOCONV_EPI_RELU 2u  /* y = max(y, 0)                                 */
@@ -73,7 +82,8 @@ typedef struct winoconv_desc {
   uint32_t epilogue;     /* WINOCONV_EPI_* bits                                              */
   int32_t gemm_engine;   /* winoconv_gemm_t                                                  */
   int32_t product_dtype; /* dtype of the Winograd-domain products: F32 (default), F16, BF16  */
-  int32_t reserved[6];
+  int32_t algo;          /* winoconv_algo_t                                                  */
+  int32_t reserved[5];
 } winoconv_desc_t;
 
 /* What winoconv_plan() derives from a descriptor. */
@@ -86,6 +96,8 @@ typedef struct winoconv_plan_info {
   int32_t positions;          /* Winograd positions summed over pieces                        */
   int32_t c_pad;              /* channel stride of the transformed operands (C rounded to 8)  */
   int32_t gemm_engine;        /* engine AUTO resolves to                                      */
+  int32_t algo;               /* algorithm AUTO resolves to (winoconv_algo_t)                 */
+  int32_t reserved0;
   int64_t tiles;              /* N * nD * nH * nW                                             */
   uint64_t filter_bytes;      /* size of the transformed filter U [positions][K][c_pad]       */
   uint64_t input_ws_bytes;    /* preferred size of the transformed-input scratch V            */

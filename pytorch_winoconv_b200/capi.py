@@ -19,6 +19,7 @@ F32, F16, BF16 = 0, 1, 2
 W_KCRS, W_RSCK = 0, 1
 GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
 EPI_BIAS, EPI_RELU, EPI_POOL2 = 1, 2, 4
+ALGO_AUTO, ALGO_STAGED, ALGO_FUSED, ALGO_ROW = 0, 1, 2, 3
 MAX_PIECES = 64
 
 # every symbol include/winoconv_b200.h declares
@@ -34,13 +35,13 @@ class Desc(Structure):
     _fields_ = [("ndim", c_int32), ("batch", c_int32), ("c_in", c_int32), ("k_out", c_int32),
                 ("in_size", c_int32 * 3), ("ker_size", c_int32 * 3), ("stride", c_int32 * 3), ("pad", c_int32 * 3),
                 ("tile_m", c_int32), ("dtype", c_int32), ("weight_layout", c_int32), ("epilogue", c_uint32),
-                ("gemm_engine", c_int32), ("product_dtype", c_int32), ("reserved", c_int32 * 6)]
+                ("gemm_engine", c_int32), ("product_dtype", c_int32), ("algo", c_int32), ("reserved", c_int32 * 5)]
 
 
 class PlanInfo(Structure):
     _fields_ = [("out_size", c_int32 * 3), ("conv_out_size", c_int32 * 3), ("tile_m", c_int32 * 3),
                 ("tiles_per_dim", c_int32 * 3), ("n_pieces", c_int32), ("positions", c_int32), ("c_pad", c_int32),
-                ("gemm_engine", c_int32), ("tiles", c_int64), ("filter_bytes", c_uint64),
+                ("gemm_engine", c_int32), ("algo", c_int32), ("reserved0", c_int32), ("tiles", c_int64), ("filter_bytes", c_uint64),
                 ("input_ws_bytes", c_uint64), ("product_ws_bytes", c_uint64), ("input_ws_bytes_min", c_uint64),
                 ("product_ws_bytes_min", c_uint64), ("block_tiles", c_int64), ("direct_flops", c_double),
                 ("gemm_flops", c_double), ("algorithmic_bytes", c_double)]
@@ -105,7 +106,7 @@ def check(status: int, what: str) -> None:
 
 
 def make_desc(*, ndim, batch, c_in, k_out, in_size, ker_size, stride=1, pad=0, tile_m=0, dtype=F16,
-              weight_layout=W_KCRS, epilogue=0, gemm_engine=GEMM_AUTO, product_dtype=F32) -> Desc:
+              weight_layout=W_KCRS, epilogue=0, gemm_engine=GEMM_AUTO, product_dtype=F32, algo=ALGO_AUTO) -> Desc:
     """Fill a descriptor.  ``in_size`` / ``ker_size`` / ``stride`` / ``pad`` have ``ndim`` entries
     (ints are broadcast); 2-D descriptors get depth 1 in slot 0."""
     def triple(v, fill):
@@ -120,7 +121,7 @@ def make_desc(*, ndim, batch, c_in, k_out, in_size, ker_size, stride=1, pad=0, t
     d.stride[:] = triple(stride, 1)
     d.pad[:] = triple(pad, 0)
     d.tile_m, d.dtype, d.weight_layout = tile_m, dtype, weight_layout
-    d.epilogue, d.gemm_engine, d.product_dtype = epilogue, gemm_engine, product_dtype
+    d.epilogue, d.gemm_engine, d.product_dtype, d.algo = epilogue, gemm_engine, product_dtype, algo
     return d
 
 

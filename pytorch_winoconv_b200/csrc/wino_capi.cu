@@ -40,20 +40,27 @@ struct DimPiece { int phase, start, r; };
 
 struct Plan {
   Geom g;
+  FGeom fg;      // filled when fused
+  bool fused;
+  bool row;      // row-piece kernel
+  RowDesc rd;
+  RowPlan rp;
   winoconv_plan_info_t info;
   int dtype, product_dtype, engine;
 };
 
-// Working set the forward aims for (V block + M block), in bytes: small enough to stay in the 126 MB L2
-// between the three kernels of a pass.  A layer whose whole V + M fits kWholeBytesLimit runs as one pass.
-// WINOCONV_BLOCK_MB / WINOCONV_WHOLE_MB override them (read once) for tuning.
+// Tiles are walked in passes of `block` tiles; V and M of a pass live in the caller's scratch.  Measured on
+// B200, passes small enough to keep V + M inside the 126 MB L2 lose more to launch gaps and under-filled
+// single-wave kernels than they save in HBM traffic (VGG-16, N = 256: 29.3 ms with 48 MB passes, 23.9 ms
+// with one pass per layer), so the default is one pass per layer up to a 16 GB scratch budget.
+// WINOCONV_BLOCK_MB / WINOCONV_WHOLE_MB override the pass budget / the whole-layer limit (read once).
 unsigned long long env_mb(const char *name, unsigned long long dflt_mb) {
   const char *v = getenv(name);
   const long long mb = (v && *v) ? atoll(v) : 0;
   return (mb > 0 ? (unsigned long long)mb : dflt_mb) << 20;
 }
-unsigned long long block_bytes_target() { static const unsigned long long v = env_mb("WINOCONV_BLOCK_MB", 48); return v; }
-unsigned long long whole_bytes_limit() { static const unsigned long long v = env_mb("WINOCONV_WHOLE_MB", 96); return v; }
+unsigned long long block_bytes_target() { static const unsigned long long v = env_mb("WINOCONV_BLOCK_MB", 16384); return v; }
+unsigned long long whole_bytes_limit() { static const unsigned long long v = env_mb("WINOCONV_WHOLE_MB", 16384); return v; }
 
 int build_plan(const winoconv_desc_t *d, Plan *plan) {
   if (!d || !plan) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null descriptor");
@@ -155,6 +162,54 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
   if (engine == WINOCONV_GEMM_TCGEN05 && d->dtype == WINOCONV_F32) return fail(WINOCONV_ERR_UNSUPPORTED, "the tcgen05 GEMM takes f16 / bf16; f32 runs on the SIMT GEMM");
   plan->dtype = d->dtype; plan->product_dtype = pdt; plan->engine = engine;
 
+  // Algorithm: the fused single-kernel path covers 16-bit F(2x2,3x3)-piece convolutions; everything else
+  // (fp32, F(4x4,3x3), the SIMT engine) runs as input transform -> batched GEMM -> output transform.
+  const bool fused_ok = d->dtype != WINOCONV_F32 && tile_m == 2 && engine == WINOCONV_GEMM_TCGEN05 &&
+                        pdt == WINOCONV_F32;
+  if (d->algo < WINOCONV_ALGO_AUTO || d->algo > WINOCONV_ALGO_ROW) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "bad algo");
+  plan->row = false;
+  if (fused_ok && (d->algo == WINOCONV_ALGO_AUTO || d->algo == WINOCONV_ALGO_ROW)) {
+    RowDesc &r = plan->rd;
+    r.N = g.N; r.C = g.C; r.K = g.K; r.D = g.D; r.H = g.H; r.W = g.W; r.oD = g.oD; r.oH = g.oH; r.oW = g.oW;
+    r.yH = g.yH; r.yW = g.yW; r.sD = g.sD; r.sH = g.sH; r.sW = g.sW; r.pD = g.pD; r.pH = g.pH; r.pW = g.pW;
+    r.kD = g.kD; r.kH = g.kH; r.kW = g.kW; r.epilogue = g.epilogue; r.weight_layout = g.weight_layout;
+    plan->row = rowfused_plan(r, &plan->rp);
+  }
+  if (d->algo == WINOCONV_ALGO_ROW && !plan->row)
+    return fail(WINOCONV_ERR_UNSUPPORTED, "the row-piece kernel needs f16 / bf16, tile_m = 2, stride 1, a kernel at most 7 taps tall, the tcgen05 engine and fp32 products");
+  if (d->algo == WINOCONV_ALGO_FUSED && !fused_ok)
+    return fail(WINOCONV_ERR_UNSUPPORTED, "the fused path needs f16 / bf16, tile_m = 2 (or 0 with a kernel other than 2-D 3x3 stride 1), the tcgen05 engine and fp32 products");
+  plan->fused = fused_ok && !plan->row && d->algo != WINOCONV_ALGO_STAGED && d->algo != WINOCONV_ALGO_ROW;
+  if (plan->fused) {
+    FGeom &f = plan->fg;
+    std::memset(&f, 0, sizeof(f));
+    f.N = g.N; f.C = g.C; f.K = g.K; f.Cp = g.Cp;
+    f.D = g.D; f.H = g.H; f.W = g.W; f.oD = g.oD; f.oH = g.oH; f.oW = g.oW; f.yH = g.yH; f.yW = g.yW;
+    f.nH = (g.oH + 1) / 2; f.nW = (g.oW + 1) / 2;
+    f.sD = g.sD; f.sH = g.sH; f.sW = g.sW; f.pD = g.pD; f.pH = g.pH; f.pW = g.pW; f.kD = g.kD; f.kH = g.kH; f.kW = g.kW;
+    f.epilogue = g.epilogue; f.weight_layout = g.weight_layout;
+    f.T = (long long)g.N * g.oD * f.nH * f.nW;
+    // windows per dimension: every polyphase part cut into 3-tap windows (the last one zero padded)
+    std::vector<std::pair<int, int>> win[2];
+    for (int i = 1; i < 3; ++i)
+      for (int phase = 0; phase < st[i]; ++phase) {
+        const int taps = (ks[i] - phase + st[i] - 1) / st[i];
+        for (int s0 = 0; s0 < taps; s0 += 3) win[i - 1].push_back({phase, s0});
+      }
+    const size_t np_f = (size_t)ks[0] * win[0].size() * win[1].size();
+    if (np_f > (size_t)kMaxFusedPieces) {
+      if (d->algo == WINOCONV_ALGO_FUSED) return fail(WINOCONV_ERR_UNSUPPORTED, "kernel decomposes into more than 160 windows");
+      plan->fused = false;
+    } else {
+      int q = 0;
+      for (int kd = 0; kd < ks[0]; ++kd) for (auto &a : win[0]) for (auto &b : win[1]) {
+        FPiece &fp = f.pieces[q++];
+        fp.kd = (int8_t)kd; fp.ph_h = (int8_t)a.first; fp.st_h = (int8_t)a.second; fp.ph_w = (int8_t)b.first; fp.st_w = (int8_t)b.second;
+      }
+      f.P = q; f.R = q * g.Cp;
+    }
+  }
+
   winoconv_plan_info_t &I = plan->info;
   for (int i = 0; i < 3; ++i) { I.conv_out_size[i] = out[i]; I.tile_m[i] = m[i]; I.tiles_per_dim[i] = nt[i]; }
   I.out_size[0] = g.yD; I.out_size[1] = g.yH; I.out_size[2] = g.yW;
@@ -171,8 +226,31 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
   const long long min_block = std::min<long long>(128, g.T);
   I.input_ws_bytes_min = v_tile * (unsigned long long)min_block;
   I.product_ws_bytes_min = m_tile * (unsigned long long)min_block;
+  I.algo = plan->fused ? WINOCONV_ALGO_FUSED : WINOCONV_ALGO_STAGED;
+  if (plan->fused) {
+    const FGeom &f = plan->fg;
+    I.tile_m[0] = 1; I.tiles_per_dim[0] = g.oD; I.tiles_per_dim[1] = f.nH; I.tiles_per_dim[2] = f.nW;
+    I.n_pieces = f.P; I.positions = 16; I.tiles = f.T;
+    I.filter_bytes = 16ull * g.K * f.R * esz;
+    I.input_ws_bytes = I.product_ws_bytes = I.input_ws_bytes_min = I.product_ws_bytes_min = 0;
+    I.block_tiles = f.T;
+  }
+  if (plan->row) {
+    const RowPlan &rp = plan->rp;
+    I.algo = WINOCONV_ALGO_ROW;
+    I.tile_m[0] = 1; I.tile_m[1] = 1; I.tile_m[2] = 2;
+    I.tiles_per_dim[0] = g.oD; I.tiles_per_dim[1] = g.oH; I.tiles_per_dim[2] = (g.oW + 1) / 2;
+    I.n_pieces = g.kD * g.kH * rp.PW; I.positions = 4;
+    I.tiles = (long long)g.N * g.oD * g.oH * ((g.oW + 1) / 2);
+    I.filter_bytes = (unsigned long long)rp.filter_elems * esz;
+    // scratch only to zero-pad the channels of x to a multiple of 8 (TMA needs 16-byte pixel strides)
+    I.input_ws_bytes = I.input_ws_bytes_min = (rp.Cp != g.C) ? (unsigned long long)g.N * g.D * g.H * g.W * rp.Cp * esz : 0ull;
+    I.product_ws_bytes = I.product_ws_bytes_min = 0;
+    I.block_tiles = I.tiles;
+  }
   I.direct_flops = 2.0 * g.N * g.K * g.C * (double)ks[0] * ks[1] * ks[2] * (double)out[0] * out[1] * out[2];
-  I.gemm_flops = 2.0 * pos * (double)g.T * g.C * g.K;
+  I.gemm_flops = plan->fused ? 2.0 * 16 * (double)plan->fg.T * plan->fg.P * g.C * g.K : 2.0 * pos * (double)g.T * g.C * g.K;
+  if (plan->row) I.gemm_flops = 2.0 * 4 * (double)I.tiles * I.n_pieces * g.C * g.K;
   I.algorithmic_bytes = (double)esz * ((double)g.N * g.D * g.H * g.W * g.C + (double)g.K * g.C * ks[0] * ks[1] * ks[2] +
                                        (double)g.N * g.yD * g.yH * g.yW * g.K);
   return WINOCONV_OK;
@@ -266,7 +344,9 @@ int winoconv_filter_transform(const winoconv_desc_t *desc, const void *weights, 
   if (st != WINOCONV_OK) return st;
   if (!weights || !u) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null weights or u");
   if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
-  cudaError_t e = launch_filter_transform(plan.g, plan.dtype, weights, u, (cudaStream_t)stream);
+  cudaError_t e = plan.row     ? launch_rowfused_filter_transform(plan.rd, plan.rp, plan.dtype, weights, u, (cudaStream_t)stream)
+                  : plan.fused ? launch_fused_filter_transform(plan.fg, plan.dtype, weights, u, (cudaStream_t)stream)
+                               : launch_filter_transform(plan.g, plan.dtype, weights, u, (cudaStream_t)stream);
   if (e != cudaSuccess) return cuda_fail(e, "filter transform launch");
   return WINOCONV_OK;
 }
@@ -277,10 +357,43 @@ static int forward_impl(const winoconv_desc_t *desc, const void *x, const void *
   Plan plan;
   int st = build_plan(desc, &plan);
   if (st != WINOCONV_OK) return st;
-  if (!x || !u || !y || !v_ws || !m_ws) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null tensor or scratch pointer");
+  if (!x || !u || !y) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null tensor pointer");
   if ((desc->epilogue & WINOCONV_EPI_BIAS) && !bias) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "EPI_BIAS set but bias is null");
-  if (!aligned16(x) || !aligned16(u) || !aligned16(y) || !aligned16(v_ws) || !aligned16(m_ws))
-    return fail(WINOCONV_ERR_INVALID_ARGUMENT, "tensors and scratch must be 16-byte aligned");
+  if (!aligned16(x) || !aligned16(u) || !aligned16(y)) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "tensors must be 16-byte aligned");
+  if (plan.row && plan.info.input_ws_bytes_min > 0) {
+    if (!v_ws || !aligned16(v_ws)) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "channel-padding scratch (v_ws) must be a 16-byte aligned pointer");
+    if (v_ws_bytes < plan.info.input_ws_bytes_min)
+      return fail(WINOCONV_ERR_WORKSPACE, "v_ws holds " + std::to_string(v_ws_bytes) + " bytes; padding the input channels needs " +
+                                              std::to_string(plan.info.input_ws_bytes_min));
+  }
+  if (plan.fused || plan.row) {   // one kernel, no V / M scratch
+    if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
+    cudaStream_t fs = (cudaStream_t)stream;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaError_t e = cudaSuccess;
+    if (stage_ms) {
+      e = cudaEventCreate(&e0);
+      if (e == cudaSuccess) e = cudaEventCreate(&e1);
+      if (e == cudaSuccess) e = cudaEventRecord(e0, fs);
+      if (e != cudaSuccess) return cuda_fail(e, "event record");
+    }
+    const char *detail = "";
+    e = plan.row ? launch_rowfused_forward(plan.rd, plan.rp, plan.dtype, x, u, bias, y, v_ws, fs, &detail)
+                 : launch_fused_forward(plan.fg, plan.dtype, x, u, bias, y, fs, &detail);
+    if (e != cudaSuccess) return cuda_fail(e, "fused forward launch", detail);
+    if (launches) *launches = (plan.row && plan.info.input_ws_bytes_min > 0) ? 2 : 1;
+    if (stage_ms) {
+      stage_ms[0] = stage_ms[2] = 0.f;
+      e = cudaEventRecord(e1, fs);
+      if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+      if (e == cudaSuccess) e = cudaEventElapsedTime(&stage_ms[1], e0, e1);
+      cudaEventDestroy(e0); cudaEventDestroy(e1);
+      if (e != cudaSuccess) return cuda_fail(e, "event timing");
+    }
+    return WINOCONV_OK;
+  }
+  if (!v_ws || !m_ws) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null scratch pointer");
+  if (!aligned16(v_ws) || !aligned16(m_ws)) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "scratch must be 16-byte aligned");
   if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
   const Geom &g = plan.g;
   const unsigned long long esz = dtype_size(plan.dtype), psz = dtype_size(plan.product_dtype);
@@ -377,6 +490,16 @@ int winoconv_forward_static(const winoconv_desc_t *desc, const void *x, const vo
   if (st != WINOCONV_OK) return st;
   if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
   const winoconv_plan_info_t &I = plan.info;
+  if (plan.fused || (plan.row && I.input_ws_bytes_min == 0))
+    return forward_impl(desc, x, u, bias, y, nullptr, 0, nullptr, 0, stream, nullptr, nullptr);
+  if (plan.row) {   // the built-in array serves as the channel-padding buffer
+    if (I.input_ws_bytes_min > WINOCONV_STATIC_SCRATCH_BYTES)
+      return fail(WINOCONV_ERR_WORKSPACE, "padding the input channels needs " + std::to_string(I.input_ws_bytes_min) +
+                                              " bytes; the built-in array holds " + std::to_string(WINOCONV_STATIC_SCRATCH_BYTES));
+    unsigned char *pad = nullptr;
+    if ((st = static_scratch_of_current_device(&pad)) != WINOCONV_OK) return st;
+    return forward_impl(desc, x, u, bias, y, pad, WINOCONV_STATIC_SCRATCH_BYTES, nullptr, 0, stream, nullptr, nullptr);
+  }
   const unsigned long long tiles_min = (unsigned long long)std::min<long long>(128, I.tiles);
   const unsigned long long v_tile = I.input_ws_bytes_min / tiles_min, m_tile = I.product_ws_bytes_min / tiles_min;
   const unsigned long long usable = WINOCONV_STATIC_SCRATCH_BYTES - 256;  // V is rounded up to the M alignment
@@ -454,9 +577,13 @@ int winoconv_add(const float *a, const float *b, float *c, int64_t n, void *stre
 
 int winoconv_read_device_error(void *stream, uint32_t *code) {
   if (!code) return fail(WINOCONV_ERR_INVALID_ARGUMENT, "null code");
-  unsigned int host = 0;
+  unsigned int host = 0, host2 = 0;
   cudaError_t e = read_and_clear_device_error((cudaStream_t)stream, &host);
+  unsigned int host3 = 0;
+  if (e == cudaSuccess) e = read_and_clear_fused_error((cudaStream_t)stream, &host2);
+  if (e == cudaSuccess) e = read_and_clear_row_error((cudaStream_t)stream, &host3);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device error word");
+  if (host == 0) host = host2 ? host2 : host3;
   *code = host;
   if (host != 0) return fail(WINOCONV_ERR_TIMEOUT, "a bounded device wait gave up, code 0x" + [&] { char b[16]; snprintf(b, sizeof b, "%x", host); return std::string(b); }());
   return WINOCONV_OK;

@@ -42,6 +42,28 @@ struct Geom {
   Piece pieces[WINOCONV_MAX_PIECES];
 };
 
+// Geometry of the fused F(2x2,3x3) kernel.  A piece is one (zero padded) 3x3 window of the kernel: depth
+// tap kd, polyphase part ph_* and first tap st_* of that part in H and W.
+struct FPiece {
+  int8_t kd, ph_h, st_h, ph_w, st_w;
+  int8_t pad_[3];
+};
+constexpr int kMaxFusedPieces = 160;   // 10 depth taps x 4 x 4 windows
+
+struct FGeom {
+  int N, C, K, Cp;
+  int P, R;             // pieces; reduction length R = P * Cp
+  int D, H, W;
+  int oD, oH, oW;       // convolution output extents
+  int yH, yW;           // stored output extents (after pooling)
+  int nH, nW;           // 2x2 tiles per image plane
+  int sD, sH, sW, pD, pH, pW, kD, kH, kW;
+  unsigned epilogue;
+  int weight_layout;
+  long long T;          // tiles: N * oD * nH * nW
+  FPiece pieces[kMaxFusedPieces];
+};
+
 // ------------------------------------------------------------------------------------------
 // element types
 // ------------------------------------------------------------------------------------------

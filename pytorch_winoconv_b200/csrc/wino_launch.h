@@ -25,6 +25,30 @@ cudaError_t launch_gemm_simt(int dtype, int product_dtype, int positions, long l
 cudaError_t launch_gemm_tcgen05(int dtype, int product_dtype, int positions, long long tiles, int c_pad, int k_out,
                                 const void *v, const void *u, void *m, cudaStream_t s, const char **detail);
 
+// Fused F(2x2,3x3) path (f16 / bf16): transformed filter u [16][K][R], then one kernel for the whole layer.
+cudaError_t launch_fused_filter_transform(const FGeom &g, int dtype, const void *w, void *u, cudaStream_t s);
+cudaError_t launch_fused_forward(const FGeom &g, int dtype, const void *x, const void *u, const void *bias, void *y,
+                                 cudaStream_t s, const char **detail);
+cudaError_t read_and_clear_fused_error(cudaStream_t s, unsigned int *code);
+
+// Row-piece DWM kernel (f16 / bf16, stride 1): 1 x 3 pieces, F(2,3) along W, taps along H / depth summed in TMEM.
+struct RowDesc {
+  int N, C, K, D, H, W, oD, oH, oW, yH, yW;
+  int sD, sH, sW, pD, pH, pW, kD, kH, kW;
+  unsigned epilogue;
+  int weight_layout;
+};
+struct RowPlan {
+  int Cp, PW, BN, CBW, RB, n_rb, n_cb, slab_rows, patch_h, patch_w, n_chunks, n_nblocks, slabs;
+  long long filter_elems, n_items;
+  int raw_bytes, a_bytes, b_stage_bytes, n_b_stages, smem_total;
+};
+bool rowfused_plan(const RowDesc &d, RowPlan *out);
+cudaError_t launch_rowfused_filter_transform(const RowDesc &d, const RowPlan &p, int dtype, const void *w, void *u, cudaStream_t s);
+cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtype, const void *x, const void *u,
+                                    const void *bias, void *y, void *pad_ws, cudaStream_t s, const char **detail);
+cudaError_t read_and_clear_row_error(cudaStream_t s, unsigned int *code);
+
 // Reads the error word of the bounded device waits, clears it and synchronises the stream.
 cudaError_t read_and_clear_device_error(cudaStream_t s, unsigned int *code);
 

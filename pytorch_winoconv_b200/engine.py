@@ -29,6 +29,20 @@ def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+class _NoScratch:
+    """Stands in for a scratch tensor when the algorithm needs none."""
+    @staticmethod
+    def data_ptr():
+        return None
+
+    @staticmethod
+    def numel():
+        return 0
+
+
+_NO_SCRATCH = _NoScratch()
+
+
 class ScratchPool:
     """Grow-only V / M scratch per device, shared by every WinoConv on that device.
 
@@ -64,7 +78,7 @@ class WinoConv:
     def __init__(self, in_shape: Sequence[int], weight: torch.Tensor, *, stride=1, padding=0, tile_m: int = 0,
                  bias: Optional[torch.Tensor] = None, relu: bool = False, pool2: bool = False,
                  gemm_engine: int = capi.GEMM_AUTO, product_dtype: Optional[torch.dtype] = None,
-                 pool: Optional[ScratchPool] = None):
+                 pool: Optional[ScratchPool] = None, algo: int = capi.ALGO_AUTO):
         if not weight.is_cuda:
             raise RuntimeError("WinoConv needs CUDA tensors: the engine has no CPU path")
         nd = weight.dim() - 2
@@ -82,7 +96,7 @@ class WinoConv:
         self.desc = capi.make_desc(ndim=nd, batch=self.in_shape[0], c_in=c, k_out=k, in_size=self.in_shape[1:-1],
                                    ker_size=tuple(weight.shape[2:]), stride=stride, pad=padding, tile_m=tile_m,
                                    dtype=dtype_code(weight.dtype), weight_layout=capi.W_KCRS, epilogue=epi,
-                                   gemm_engine=gemm_engine, product_dtype=pdt)
+                                   gemm_engine=gemm_engine, product_dtype=pdt, algo=algo)
         self.info = capi.plan(self.desc)
         out_sp = list(self.info.out_size)[3 - nd:]
         self.out_shape = (self.in_shape[0], *out_sp, k)
@@ -107,17 +121,26 @@ class WinoConv:
             out = torch.empty(self.out_shape, dtype=self.dtype, device=self.device)
         elif tuple(out.shape) != self.out_shape or out.dtype != self.dtype or not out.is_contiguous():
             raise ValueError(f"out must be contiguous {self.out_shape} {self.dtype}")
-        v, m = self.pool.get(self.device, int(self.info.input_ws_bytes), int(self.info.product_ws_bytes))
+        v, m = self._scratch()
         with torch.cuda.device(self.device):
             capi.forward(self.desc, x.data_ptr(), self.u.data_ptr(), None if self.bias is None else self.bias.data_ptr(),
                          out.data_ptr(), v.data_ptr(), v.numel(), m.data_ptr(), m.numel(), _stream_ptr(self.device))
         return out
 
+    def _scratch(self):
+        """V / M scratch for the staged algorithm; the fused kernel needs none."""
+        if self.info.algo == capi.ALGO_FUSED or (self.info.algo == capi.ALGO_ROW and self.info.input_ws_bytes == 0):
+            return _NO_SCRATCH, _NO_SCRATCH
+        if self.info.algo == capi.ALGO_ROW:          # channel-padding buffer only
+            v, _ = self.pool.get(self.device, int(self.info.input_ws_bytes), 16)
+            return v, _NO_SCRATCH
+        return self.pool.get(self.device, int(self.info.input_ws_bytes), int(self.info.product_ws_bytes))
+
     def timed(self, x: torch.Tensor, out: Optional[torch.Tensor] = None):
         """Forward with CUDA events around the three stages: (y, [ms_in, ms_gemm, ms_out], launches)."""
         if out is None:
             out = torch.empty(self.out_shape, dtype=self.dtype, device=self.device)
-        v, m = self.pool.get(self.device, int(self.info.input_ws_bytes), int(self.info.product_ws_bytes))
+        v, m = self._scratch()
         with torch.cuda.device(self.device):
             ms, n = capi.forward_timed(self.desc, x.data_ptr(), self.u.data_ptr(),
                                        None if self.bias is None else self.bias.data_ptr(), out.data_ptr(),
@@ -127,6 +150,10 @@ class WinoConv:
     @property
     def launches_per_call(self) -> int:
         """Kernels this forward launches: three per pass over a block of tiles."""
+        if self.info.algo == capi.ALGO_FUSED:
+            return 1
+        if self.info.algo == capi.ALGO_ROW:
+            return 2 if self.info.input_ws_bytes else 1
         blocks = -(-int(self.info.tiles) // int(self.info.block_tiles))
         return 3 * blocks
 
@@ -161,7 +188,8 @@ class VGG16ConvStack:
     transforms.  Input ``[N, H, W, 3]`` channels-last; output ``[N, H/32, W/32, 512]``."""
 
     def __init__(self, weights: Sequence[torch.Tensor], batch: int, height: int = 224, width: int = 224,
-                 tile_m: int = 0, product_dtype: Optional[torch.dtype] = None, gemm_engine: int = capi.GEMM_AUTO):
+                 tile_m: int = 0, product_dtype: Optional[torch.dtype] = None, gemm_engine: int = capi.GEMM_AUTO,
+                 algo: int = capi.ALGO_AUTO):
         if len(weights) != 13:
             raise ValueError("VGG-16 has 13 convolutions")
         self.layers: List[WinoConv] = []
@@ -172,7 +200,8 @@ class VGG16ConvStack:
         for i, wt in enumerate(weights):
             cin = int(wt.shape[1])
             conv = WinoConv((batch, h, w, cin), wt, padding=1, tile_m=tile_m, relu=True,
-                            pool2=i in VGG16_POOL_AFTER, product_dtype=product_dtype, gemm_engine=gemm_engine)
+                            pool2=i in VGG16_POOL_AFTER, product_dtype=product_dtype, gemm_engine=gemm_engine,
+                            algo=algo)
             self.layers.append(conv)
             self.acts.append(torch.empty(conv.out_shape, dtype=dt, device=dev))
             h, w = conv.out_shape[1], conv.out_shape[2]

@@ -14,14 +14,14 @@ def seeded(shape, seed, dist="normal", dtype=torch.float32):
 
 
 def run_engine(x, w, *, stride=1, padding=0, tile_m=0, bias=None, relu=False, pool2=False, gemm_engine=capi.GEMM_AUTO,
-               product_dtype=None):
+               product_dtype=None, algo=capi.ALGO_AUTO):
     """x [N,C,*sp], w [K,C,*k] on CPU in the target dtype -> device result as [N,K,*out] on CPU."""
     nd = w.dim() - 2
     dev = torch.device("cuda", 0)
     xl = x.permute(0, *range(2, 2 + nd), 1).contiguous().to(dev)
     conv = engine.WinoConv(xl.shape, w.to(dev), stride=stride, padding=padding, tile_m=tile_m,
                            bias=None if bias is None else bias.to(dev), relu=relu, pool2=pool2,
-                           gemm_engine=gemm_engine, product_dtype=product_dtype)
+                           gemm_engine=gemm_engine, product_dtype=product_dtype, algo=algo)
     y = conv(xl)
     torch.cuda.synchronize()
     assert capi.read_device_error() == 0

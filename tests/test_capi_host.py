@@ -28,9 +28,9 @@ BASELINE_CONFIGS = [
     # name, kwargs, expected (positions, pieces, tiles)
     ("cfg1", dict(ndim=2, batch=8, c_in=64, k_out=64, in_size=(56, 56), ker_size=3, pad=1, tile_m=2, dtype=capi.F32), (16, 1, 6272)),
     ("cfg2", dict(ndim=2, batch=32, c_in=256, k_out=256, in_size=(28, 28), ker_size=3, pad=1, tile_m=4), (36, 1, 1568)),
-    ("cfg3a", dict(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3), (100, 9, 200704)),
-    ("cfg3b", dict(ndim=2, batch=32, c_in=128, k_out=128, in_size=(56, 56), ker_size=5, pad=2), (49, 4, 25088)),
-    ("cfg4", dict(ndim=3, batch=8, c_in=64, k_out=64, in_size=(16, 56, 56), ker_size=3, pad=1), (64, 1, 50176)),
+    ("cfg3a", dict(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3, algo=capi.ALGO_STAGED), (100, 9, 200704)),
+    ("cfg3b", dict(ndim=2, batch=32, c_in=128, k_out=128, in_size=(56, 56), ker_size=5, pad=2, algo=capi.ALGO_STAGED), (49, 4, 25088)),
+    ("cfg4", dict(ndim=3, batch=8, c_in=64, k_out=64, in_size=(16, 56, 56), ker_size=3, pad=1, algo=capi.ALGO_STAGED), (64, 1, 50176)),
 ]
 
 
@@ -47,6 +47,56 @@ def test_plan_matches_survey_figures(name, kw, expect):
         ks *= k
     assert info.direct_flops == pytest.approx(2.0 * d.batch * d.k_out * d.c_in * ks * n_out)
     assert info.gemm_flops == pytest.approx(2.0 * info.positions * info.tiles * d.c_in * d.k_out)
+    assert info.algo == capi.ALGO_STAGED
+
+
+@pytest.mark.parametrize("kw,windows,tiles", [
+    (dict(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3), 9, 64 * 56 * 56),
+    (dict(ndim=2, batch=32, c_in=128, k_out=128, in_size=(56, 56), ker_size=5, pad=2), 4, 32 * 28 * 28),
+    (dict(ndim=3, batch=8, c_in=64, k_out=64, in_size=(16, 56, 56), ker_size=3, pad=1), 3, 8 * 16 * 28 * 28),
+    (dict(ndim=2, batch=2, c_in=16, k_out=16, in_size=(9, 9), ker_size=3, pad=1, tile_m=2), 1, 2 * 5 * 5),
+])
+def test_fused_plan(kw, windows, tiles):
+    """The 3x3-piece fused kernel: 16 positions, every piece a 3x3 window in the GEMM reduction, depth taps
+    applied directly, no scratch."""
+    d = capi.make_desc(**{**kw, "algo": capi.ALGO_FUSED})
+    info = capi.plan(d)
+    assert info.algo == capi.ALGO_FUSED
+    assert (info.positions, info.n_pieces, info.tiles) == (16, windows, tiles)
+    assert info.input_ws_bytes == 0 and info.product_ws_bytes == 0
+    assert info.filter_bytes == 16 * d.k_out * windows * info.c_pad * 2
+    assert info.gemm_flops == pytest.approx(2.0 * 16 * tiles * windows * d.c_in * d.k_out)
+
+
+def test_row_piece_plan():
+    """AUTO picks the row-piece kernel for 16-bit stride-1 convolutions: 4 positions, kD*kH*ceil(kW/3) pieces."""
+    d = capi.make_desc(ndim=2, batch=32, c_in=128, k_out=128, in_size=(56, 56), ker_size=5, pad=2)
+    info = capi.plan(d)
+    assert info.algo == capi.ALGO_ROW and (info.positions, info.n_pieces) == (4, 10)
+    assert info.tiles == 32 * 56 * 28 and info.input_ws_bytes == 0 and info.product_ws_bytes == 0
+    assert info.filter_bytes == 10 * 4 * 128 * 128 * 2
+    assert info.gemm_flops == pytest.approx(2.0 * 4 * info.tiles * 10 * 128 * 128)
+    d3 = capi.make_desc(ndim=3, batch=8, c_in=64, k_out=64, in_size=(16, 56, 56), ker_size=3, pad=1)
+    i3 = capi.plan(d3)
+    assert i3.algo == capi.ALGO_ROW and i3.n_pieces == 9
+    rgb = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=3, k_out=64, in_size=(224, 224), ker_size=3, pad=1, tile_m=2))
+    assert rgb.algo == capi.ALGO_ROW and rgb.c_pad == 8 and rgb.input_ws_bytes == 4 * 224 * 224 * 8 * 2
+    s2 = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=16, k_out=64, in_size=(64, 64), ker_size=7, stride=2, pad=3))
+    assert s2.algo == capi.ALGO_FUSED                       # stride 2 falls to the 3x3-piece kernel
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.plan(capi.make_desc(ndim=2, batch=4, c_in=16, k_out=64, in_size=(64, 64), ker_size=7, stride=2, pad=3, algo=capi.ALGO_ROW))
+    assert ei.value.status == capi.ERR_UNSUPPORTED
+
+
+def test_fused_refused_where_it_does_not_apply():
+    for kw in (dict(dtype=capi.F32), dict(tile_m=4), dict(gemm_engine=capi.GEMM_SIMT), dict(product_dtype=capi.F16)):
+        base = dict(ndim=2, batch=1, c_in=8, k_out=8, in_size=(16, 16), ker_size=3, algo=capi.ALGO_FUSED)
+        base.update(kw)
+        with pytest.raises(capi.WinoconvError) as ei:
+            capi.plan(capi.make_desc(**base))
+        assert ei.value.status == capi.ERR_UNSUPPORTED
+    auto = capi.plan(capi.make_desc(ndim=2, batch=1, c_in=8, k_out=8, in_size=(16, 16), ker_size=3, dtype=capi.F32))
+    assert auto.algo == capi.ALGO_STAGED
 
 
 @pytest.mark.parametrize("ks,stride", [((5, 5), 1), ((7, 7), 1), ((7, 7), 2), ((9, 9), 1), ((4, 4), 1), ((3, 4), 1),
@@ -89,6 +139,7 @@ def test_tile_counts_and_output_sizes():
     (dict(dtype=capi.F32, gemm_engine=capi.GEMM_TCGEN05), capi.ERR_UNSUPPORTED),
     (dict(dtype=capi.F16, product_dtype=capi.BF16), capi.ERR_UNSUPPORTED),
     (dict(epilogue=64), capi.ERR_INVALID_ARGUMENT),
+    (dict(algo=9), capi.ERR_INVALID_ARGUMENT),
 ])
 def test_bad_descriptors_return_status_not_exit(kw, status):
     base = dict(ndim=2, batch=1, c_in=8, k_out=8, in_size=(16, 16), ker_size=3)

@@ -39,10 +39,93 @@ SMALL = [
 @pytest.mark.parametrize("n,c,k,sp,ks,stride,pad,m", SMALL)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_small_cases(n, c, k, sp, ks, stride, pad, m, dtype):
+    """Staged algorithm (input transform -> batched GEMM -> output transform)."""
     x = seeded((n, c) + sp, 11, dtype=dtype)
     w = wo.kaiming_normal((k, c) + ks, 12).to(dtype)
-    y, _ = run_engine(x, w, stride=stride, padding=pad, tile_m=m)
+    y, conv = run_engine(x, w, stride=stride, padding=pad, tile_m=m, algo=capi.ALGO_STAGED)
+    assert conv.info.algo == capi.ALGO_STAGED
     check_against_oracle(x, w, y, stride=stride, padding=pad)
+
+
+FUSED_EXTRA = [
+    (3, 64, 64, (20, 24), (3, 3), 1, 1, 2),        # several work items, two channel blocks
+    (2, 72, 40, (17, 15), (3, 3), 1, 1, 2),        # reduction slab tail, K not a block multiple
+    (1, 160, 96, (12, 12), (5, 5), 1, 2, 2),       # windows straddling 64-wide slabs
+    (5, 16, 8, (30, 31), (3, 3), 1, 1, 2),         # tiles not a multiple of 128
+    (1, 8, 36, (9, 9), (3, 3), 1, 1, 2),           # K = 36: 16-byte stores with a partial last block
+    (1, 8, 30, (9, 9), (3, 3), 1, 1, 2),           # K not a multiple of 8: element-wise stores
+    (2, 3, 64, (30, 28), (3, 3), 1, 1, 2),         # RGB first layer: few-channel FMA variant
+    (1, 4, 10, (11, 12), (5, 5), 1, 2, 2),         # few channels, K not a multiple of 4
+    (1, 1, 520, (9, 9), (3, 3), 1, 1, 2),          # too many output channels for the few-channel variant
+]
+
+
+@pytest.mark.parametrize("n,c,k,sp,ks,stride,pad,m", [c for c in SMALL if c[7] != 4] + FUSED_EXTRA)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_cases(n, c, k, sp, ks, stride, pad, m, dtype):
+    """Fused single-kernel algorithm on the same shapes (every DWM piece shape, stride 2, 3-D, ragged edges)."""
+    x = seeded((n, c) + sp, 11, dtype=dtype)
+    w = wo.kaiming_normal((k, c) + ks, 12).to(dtype)
+    y, conv = run_engine(x, w, stride=stride, padding=pad, tile_m=2, algo=capi.ALGO_FUSED)
+    assert conv.info.algo == capi.ALGO_FUSED and conv.info.positions == 16
+    check_against_oracle(x, w, y, stride=stride, padding=pad)
+
+
+ROW_CASES = [c for c in SMALL + FUSED_EXTRA if c[5] == 1 and c[7] != 4 and c[4][-2] <= 7] + [
+    (2, 32, 64, (16, 64), (3, 3), 1, 1, 2),        # exactly one 8 x 16 block per image, one channel slab
+    (1, 64, 128, (40, 70), (3, 3), 1, 1, 2),       # N = 128 accumulators, ragged blocks in both directions
+    (2, 96, 192, (14, 14), (3, 3), 1, 1, 2),       # 16 x 8 block shape, two channel blocks, slab tail
+    (1, 40, 72, (9, 50), (3, 3), 1, 0, 2),         # no padding, K not a block multiple
+    (1, 16, 16, (12, 12), (7, 7), 1, 3, 2),        # tallest kernel the row kernel takes
+]
+
+
+@pytest.mark.parametrize("n,c,k,sp,ks,stride,pad,m", ROW_CASES)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_row_piece_cases(n, c, k, sp, ks, stride, pad, m, dtype):
+    """Row-piece kernel (1 x 3 DWM pieces; F(2,3) along W, taps along H / depth summed in TMEM)."""
+    x = seeded((n, c) + sp, 11, dtype=dtype)
+    w = wo.kaiming_normal((k, c) + ks, 12).to(dtype)
+    y, conv = run_engine(x, w, stride=stride, padding=pad, tile_m=2, algo=capi.ALGO_ROW)
+    assert conv.info.algo == capi.ALGO_ROW and conv.info.positions == 4
+    check_against_oracle(x, w, y, stride=stride, padding=pad)
+
+
+def test_row_piece_epilogue_bias_relu_pool():
+    for hw in ((13, 14), (32, 64), (16, 16)):
+        x = seeded((2, 16) + hw, 31, dtype=torch.float16)
+        w = wo.kaiming_normal((72, 16, 3, 3), 32).half()
+        b = seeded((72,), 33, dtype=torch.float16)
+        o = wo.direct_conv_f64(x, w, padding=1) + b.double().view(1, -1, 1, 1)
+        y, conv = run_engine(x, w, padding=1, tile_m=2, bias=b, relu=True, algo=capi.ALGO_ROW)
+        assert conv.info.algo == capi.ALGO_ROW
+        assert wo.error_metrics(y, torch.relu(o))["E_A"] < 5e-3
+        y, _ = run_engine(x, w, padding=1, tile_m=2, bias=b, relu=True, pool2=True, algo=capi.ALGO_ROW)
+        op = torch.nn.functional.max_pool2d(torch.relu(o), 2)
+        assert tuple(y.shape) == tuple(op.shape)
+        assert wo.error_metrics(y, op)["E_A"] < 5e-3
+
+
+def test_fused_epilogue_bias_relu_pool():
+    x = seeded((2, 16, 13, 14), 31, dtype=torch.float16)
+    w = wo.kaiming_normal((40, 16, 3, 3), 32).half()
+    b = seeded((40,), 33, dtype=torch.float16)
+    o = wo.direct_conv_f64(x, w, padding=1) + b.double().view(1, -1, 1, 1)
+    y, conv = run_engine(x, w, padding=1, tile_m=2, bias=b, relu=True, algo=capi.ALGO_FUSED)
+    assert conv.info.algo == capi.ALGO_FUSED
+    assert wo.error_metrics(y, torch.relu(o))["E_A"] < 5e-3
+    y, _ = run_engine(x, w, padding=1, tile_m=2, bias=b, relu=True, pool2=True, algo=capi.ALGO_FUSED)
+    op = torch.nn.functional.max_pool2d(torch.relu(o), 2)
+    assert tuple(y.shape) == tuple(op.shape) == (2, 40, 6, 7)
+    assert wo.error_metrics(y, op)["E_A"] < 5e-3
+
+
+def test_fused_and_staged_agree():
+    x = seeded((4, 64, 28, 28), 71, dtype=torch.float16)
+    w = wo.kaiming_normal((64, 64, 3, 3), 72).half()
+    yf, _ = run_engine(x, w, padding=1, tile_m=2, algo=capi.ALGO_FUSED)
+    ys, _ = run_engine(x, w, padding=1, tile_m=2, algo=capi.ALGO_STAGED)
+    assert wo.error_metrics(yf, ys.double())["E_B"] < 5e-3
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -76,7 +159,7 @@ def test_blocked_passes_equal_single_pass():
     w = wo.kaiming_normal((16, 16, 3, 3), 42).half()
     dev = torch.device("cuda", 0)
     xl = x.permute(0, 2, 3, 1).contiguous().to(dev)
-    conv = engine.WinoConv(xl.shape, w.to(dev), padding=1)
+    conv = engine.WinoConv(xl.shape, w.to(dev), padding=1)      # F(4x4,3x3): staged
     y_full = conv(xl).clone()
     v = torch.empty(int(conv.info.input_ws_bytes_min) * 2, dtype=torch.uint8, device=dev)
     m = torch.empty(int(conv.info.product_ws_bytes_min) * 2, dtype=torch.uint8, device=dev)
@@ -113,28 +196,45 @@ def test_cfg2_fp16_f43(product_dtype):
     print("cfg2 engine", product_dtype, err)
 
 
-def test_cfg3a_fp16_7x7_stride2():
+ALGOS = [(capi.ALGO_STAGED, "staged"), (capi.ALGO_FUSED, "fused"), (capi.ALGO_ROW, "row")]
+
+
+@pytest.mark.parametrize("algo,name", ALGOS[:2])      # stride 2: the row-piece kernel does not apply
+def test_cfg3a_fp16_7x7_stride2(algo, name):
     x = seeded((64, 3, 224, 224), 0, dist="uniform", dtype=torch.float16)
     w = wo.kaiming_normal((64, 3, 7, 7), 1).half()
-    y, conv = run_engine(x, w, stride=2, padding=3)
-    assert conv.info.n_pieces == 9 and conv.info.positions == 100
-    print("cfg3a engine", check_against_oracle(x, w, y, stride=2, padding=3))
+    y, conv = run_engine(x, w, stride=2, padding=3, algo=algo)
+    assert (conv.info.n_pieces, conv.info.positions) == ((9, 100) if algo == capi.ALGO_STAGED else (9, 16))
+    print("cfg3a engine", name, check_against_oracle(x, w, y, stride=2, padding=3))
 
 
-def test_cfg3b_fp16_5x5():
+@pytest.mark.parametrize("algo,name", ALGOS)
+def test_cfg3b_fp16_5x5(algo, name):
     x = seeded((32, 128, 56, 56), 0, dtype=torch.float16)
     w = wo.kaiming_normal((128, 128, 5, 5), 1).half()
-    y, conv = run_engine(x, w, padding=2)
-    assert conv.info.n_pieces == 4 and conv.info.positions == 49
-    print("cfg3b engine", check_against_oracle(x, w, y, padding=2))
+    y, conv = run_engine(x, w, padding=2, algo=algo)
+    assert (conv.info.n_pieces, conv.info.positions) == {capi.ALGO_STAGED: (4, 49), capi.ALGO_FUSED: (4, 16), capi.ALGO_ROW: (10, 4)}[algo]
+    print("cfg3b engine", name, check_against_oracle(x, w, y, padding=2))
 
 
-def test_cfg4_fp16_3d():
+@pytest.mark.parametrize("algo,name", ALGOS)
+def test_cfg4_fp16_3d(algo, name):
     x = seeded((8, 64, 16, 56, 56), 0, dtype=torch.float16)
     w = wo.kaiming_normal((64, 64, 3, 3, 3), 1).half()
-    y, conv = run_engine(x, w, padding=1)
-    assert conv.info.positions == 64
-    print("cfg4 engine", check_against_oracle(x, w, y, padding=1))
+    y, conv = run_engine(x, w, padding=1, algo=algo)
+    assert (conv.info.n_pieces, conv.info.positions) == {capi.ALGO_STAGED: (1, 64), capi.ALGO_FUSED: (3, 16), capi.ALGO_ROW: (9, 4)}[algo]
+    print("cfg4 engine", name, check_against_oracle(x, w, y, padding=1))
+
+
+def test_auto_resolves_to_fused_for_16bit_f2_and_staged_otherwise():
+    x = seeded((1, 8, 12, 12), 1, dtype=torch.float16)
+    w5 = wo.kaiming_normal((8, 8, 5, 5), 2).half()
+    w3 = wo.kaiming_normal((8, 8, 3, 3), 3).half()
+    assert run_engine(x, w5, padding=2)[1].info.algo == capi.ALGO_ROW
+    assert run_engine(x, w5, padding=2, stride=2)[1].info.algo == capi.ALGO_FUSED   # stride 2: 3x3 pieces
+    assert run_engine(x, w3, padding=1)[1].info.algo == capi.ALGO_STAGED          # auto tile_m = 4
+    assert run_engine(x, w3, padding=1, tile_m=2)[1].info.algo == capi.ALGO_ROW
+    assert run_engine(x.float(), w3.float(), padding=1, tile_m=2)[1].info.algo == capi.ALGO_STAGED
 
 
 def test_linearity_at_full_size():

@@ -39,6 +39,7 @@ def test_static_scratch_forward_matches_on_consecutive_calls():
     # layer A needs several passes through the 32 MiB array; layer B is a different shape and dtype
     xa, ca = _layer(1, 16, 64, 96, 56, 3, 1, torch.float16)
     xb, cb = _layer(2, 2, 24, 40, 21, 5, 2, torch.float32)
+    assert ca.info.algo == capi.ALGO_STAGED and cb.info.algo == capi.ALGO_STAGED
     need_a = int(ca.info.tiles) * (int(ca.info.input_ws_bytes_min) + int(ca.info.product_ws_bytes_min)) // 128
     assert need_a > capi.STATIC_SCRATCH_BYTES            # so the array is reused within one call
     errs = [_both(xa, ca), _both(xb, cb), _both(xa, ca)]
@@ -47,7 +48,7 @@ def test_static_scratch_forward_matches_on_consecutive_calls():
 
 def test_static_scratch_refuses_oversized_layers():
     # 3-D 3x3x3 with 1024 -> 1024 channels: 64 positions x (1024*2 + 1024*4) B x 128 tiles = 48 MiB > 32 MiB (512 tiles in all)
-    d = capi.make_desc(ndim=3, batch=1, c_in=1024, k_out=1024, in_size=(16, 16, 16), ker_size=3, pad=1)
+    d = capi.make_desc(ndim=3, batch=1, c_in=1024, k_out=1024, in_size=(16, 16, 16), ker_size=3, pad=1, algo=capi.ALGO_STAGED)
     with pytest.raises(capi.WinoconvError) as ei:
         capi.forward_static(d, 256, 256, None, 256)
     assert ei.value.status == capi.ERR_WORKSPACE
