@@ -60,7 +60,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg2"])
+    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg2", "conv"])
+    ap.add_argument("--shape", default="256,256,56,3", help="--workload conv: C,K,HW,kernel (stride 1, 'same' padding, fp16)")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: 256 for vgg16, 32 for cfg2)")
     ap.add_argument("--algo", default="auto", choices=["auto", "row", "fused", "staged"],
                     help="fused: one tcgen05 kernel per layer, F(2x2,3x3); staged: three kernels per pass, F(4x4,3x3)")
@@ -259,10 +260,11 @@ def run_ours(args):
     else:
         from oracle import winograd_oracle as wo   # Kaiming-normal helper only; nothing timed runs in the oracle
         batch = args.batch or 32
-        w = wo.kaiming_normal((256, 256, 3, 3), 1).half().to(dev)
+        cc, kk, hw, ksz = (256, 256, 28, 3) if args.workload == "cfg2" else tuple(int(v) for v in args.shape.split(","))
+        w = wo.kaiming_normal((kk, cc, ksz, ksz), 1).half().to(dev)
         fused = args.algo in ("fused", "row")
         algo_code = {"auto": capi.ALGO_STAGED, "row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
-        conv = engine.WinoConv((batch, 28, 28, 256), w, padding=1, tile_m=2 if fused else 4, algo=algo_code,
+        conv = engine.WinoConv((batch, hw, hw, cc), w, padding=ksz // 2, tile_m=2 if (fused or ksz != 3) else 4, algo=algo_code,
                                product_dtype=torch.float16 if (args.product == "f16" and not fused) else None)
         out_buf = torch.empty(conv.out_shape, dtype=torch.float16, device=dev)
 
@@ -282,9 +284,10 @@ def run_ours(args):
             acts = [out_buf]
 
         model = _Single()
-        x_host = torch.randn(batch, 28, 28, 256, generator=g).half().pin_memory()
+        x_host = torch.randn(batch, hw, hw, cc, generator=g).half().pin_memory()
         layers = model.layers
-        workload = "conv3x3_n32_c256_k256_28x28_f43 (BASELINE configs[1])"
+        workload = ("conv3x3_n32_c256_k256_28x28_f43 (BASELINE configs[1])" if args.workload == "cfg2"
+                    else f"conv{ksz}x{ksz}_n{batch}_c{cc}_k{kk}_{hw}x{hw}")
         metric = "conv_images_per_s"
     x_dev = x_host.to(dev, non_blocking=True)
     y_host = torch.empty(model.out_shape, dtype=torch.float16).pin_memory()

@@ -39,9 +39,9 @@ struct RowDesc {
   int weight_layout;
 };
 struct RowPlan {
-  int Cp, PW, BN, CBW, RB, n_rb, n_cb, slab_rows, patch_h, patch_w, n_chunks, n_nblocks, slabs;
+  int Cp, PW, BN, MB, CBW, RB, n_rb, n_cb, slab_rows, patch_h, patch_w, n_chunks, n_nblocks, slabs;
   long long filter_elems, n_items;
-  int raw_bytes, a_bytes, b_stage_bytes, n_b_stages, smem_total;
+  int raw_bytes, a_bytes, b_stage_bytes, n_b_stages, n_a_bufs, smem_total;
 };
 bool rowfused_plan(const RowDesc &d, RowPlan *out);
 cudaError_t launch_rowfused_filter_transform(const RowDesc &d, const RowPlan &p, int dtype, const void *w, void *u, cudaStream_t s);

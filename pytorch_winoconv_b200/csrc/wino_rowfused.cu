@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "wino_common.cuh"
 #include "wino_launch.h"
@@ -33,6 +34,11 @@
 namespace wino {
 
 __device__ unsigned int g_row_error = 0;
+
+#ifdef WINO_ROW_TRACE
+// Development aid (not built by default): per-role accumulated wait clocks of CTA 0.
+__device__ unsigned long long g_row_trace[32];
+#endif
 
 namespace rowf {
 
@@ -67,10 +73,41 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Polling wait (non-blocking test_wait) for the two threads on the MMA critical path.
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long start = clock64();
+  unsigned spins = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (*abort_word != 0u) return false;
+      if (clock64() - start > WAIT_LIMIT_CLOCKS) {
+        *abort_word = code;
+        atomicCAS(&g_row_error, 0u, code);
+        return false;
+      }
+    }
+  }
+#ifdef WINO_ROW_TRACE
+  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_row_trace[code & 15u], (unsigned long long)(clock64() - start));
+#endif
+  return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code,
+                                          bool backoff = false) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
+    if (backoff) __nanosleep(200);     // roles with slack yield their issue slots to the MMA thread
     if (*abort_word != 0u) return false;
     if (clock64() - start > WAIT_LIMIT_CLOCKS) {
       *abort_word = code;
@@ -78,6 +115,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+#ifdef WINO_ROW_TRACE
+  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_row_trace[code & 15u], (unsigned long long)(clock64() - start));
+#endif
   return true;
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
@@ -100,6 +140,21 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same MMA with the descriptors given as (low word, high word): the high word is a constant of the layout,
+// so the issuing thread only does 32-bit adds on the low words between MMAs.  (One thread issues every MMA of
+// the CTA; with the descriptors rebuilt per instruction its dependent-issue latency, not the tensor pipe, set
+// the pace -- about 150 clocks per MMA instead of 64.)
+constexpr uint32_t DESC_HI_SW64 = (uint32_t)(512 >> 4) | (1u << 14) | (4u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ void umma_f16_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_HI_SW64), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -154,7 +209,7 @@ __device__ __forceinline__ void store16(T *dst, const float (&v)[16], int kbase,
 // Shared-memory carve-up computed on the host and passed in (all offsets from the 1024-aligned base).
 struct Smem {
   int raw_bytes, a_bytes, b_stage_bytes;   // one raw patch; one set of four slabs; one stage of four filter slabs
-  int n_b_stages;
+  int n_b_stages, n_a_bufs;
   int off_raw[2], off_a[2], off_b, off_bars;
   int total;
 };
@@ -165,22 +220,25 @@ struct RGeom {
   int pD, pH, pW, kD, kH, kW;
   int PW;                 // F(2,3) windows along W: ceil(kW / 3)
   int RB, CBW;            // tile block: RB output rows x CBW column pairs, RB * CBW == 128
+  int MB;                 // tile blocks per work item, stacked along H (they share every filter slab)
   int n_rb, n_cb;         // blocks per image plane
-  int slab_rows;          // (RB + kH - 1) * CBW
+  int slab_rows;          // (MB * RB + kH - 1) * CBW
   int patch_h, patch_w;   // raw patch extents (pixels)
   int n_chunks;           // ceil(C / 32)
   int n_nblocks;
   long long n_items;
   unsigned epilogue;
+  unsigned dbg;           // timing experiments only (WINOCONV_ROW_DBG): 1 no filter TMA, 2 no input TMA, 4 no transform, 8 no MMA, 16 no stores
 };
 
-template <typename T, int BN>
+template <typename T, int BN, int MB>
 __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                  const __grid_constant__ CUtensorMap map_u,
                                                                  T *__restrict__ y, const T *__restrict__ bias,
                                                                  const __grid_constant__ RGeom g,
                                                                  const __grid_constant__ Smem sl, uint32_t idesc) {
-  constexpr int ACC_BUFS = (BN == 64) ? 2 : 1;           // 4 positions x BN columns per buffer
+  constexpr int ACC_COLS = MB * 4 * BN;                  // MB blocks x 4 positions x BN columns per buffer
+  constexpr int ACC_BUFS = (ACC_COLS <= 256) ? 2 : 1;
   extern __shared__ uint8_t smem_raw_[];
   const uint32_t raw0 = smem_u32(smem_raw_);
   const uint32_t base = (raw0 + 1023u) & ~1023u;
@@ -199,6 +257,9 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + sl.off_bars + 260);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef WINO_ROW_TRACE
+  const long long trace_kernel_t0 = clock64();
+#endif
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(raw_full(i), 1);
@@ -245,9 +306,10 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks; ++ch) {
             const int s = it & 1;
-            if (!mbar_wait(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
+            if (!mbar_wait(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY, (g.dbg & 32u) != 0)) { alive = false; break; }
+            if (g.dbg & 2u) { mbar_arrive(raw_full(s)); ++it; continue; }
             mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
-            tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * g.RB - g.pH,
+            tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
                         od + kd - g.pD, n);
             ++it;
           }
@@ -263,14 +325,14 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x) {
       for (int step = 0; step < steps_per_item && alive; ++step) {
         const int rs = it_raw & 1;
-        if (!mbar_wait(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW)) { alive = false; break; }
+        if (!mbar_wait(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW, (g.dbg & 32u) != 0)) { alive = false; break; }
         const uint8_t *raw = base_ptr + sl.off_raw[rs];
         for (int w = 0; w < g.PW && alive; ++w) {
-          const int as = it_a & 1;
-          if (!mbar_wait(a_empty(as), ((it_a >> 1) & 1u) ^ 1u, abort_word, ERR_PROD_A)) { alive = false; break; }
+          const int as = (int)(it_a % (uint32_t)sl.n_a_bufs);
+          if (!mbar_wait(a_empty(as), ((it_a / (uint32_t)sl.n_a_bufs) & 1u) ^ 1u, abort_word, ERR_PROD_A, (g.dbg & 32u) != 0)) { alive = false; break; }
           uint8_t *slab = base_ptr + sl.off_a[as];
           const int slab_bytes = g.slab_rows * 64;
-          for (int row = ptid >> 2; row < n_tasks; row += N_PROD / 4) {
+          for (int row = ptid >> 2; row < ((g.dbg & 4u) ? 0 : n_tasks); row += N_PROD / 4) {
             const int ir = row / g.CBW, cp = row - ir * g.CBW;
             const uint8_t *src = raw + ((size_t)(ir * g.patch_w + 2 * cp + 3 * w) * KC + v * 8) * 2;
             V8<T> d0, d1, d2, d3;
@@ -308,7 +370,8 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             for (int w = 0; w < g.PW && alive; ++w)
               for (int kh = 0; kh < g.kH; ++kh) {
                 const int s = it % nbs;
-                if (!mbar_wait(b_empty(s), ((it / nbs) & 1u) ^ 1u, abort_word, ERR_B_EMPTY)) { alive = false; break; }
+                if (!((g.dbg & 64u) ? mbar_poll(b_empty(s), ((it / nbs) & 1u) ^ 1u, abort_word, ERR_B_EMPTY) : mbar_wait(b_empty(s), ((it / nbs) & 1u) ^ 1u, abort_word, ERR_B_EMPTY, (g.dbg & 32u) != 0))) { alive = false; break; }
+                if (g.dbg & 1u) { mbar_arrive(b_full(s)); ++it; continue; }
                 mbar_expect_tx(b_full(s), (uint32_t)sl.b_stage_bytes);
                 const int slab0 = ((kd * g.kH + kh) * g.PW + w) * 4;
 #pragma unroll
@@ -327,44 +390,72 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     if (lane == 0) {
       uint32_t it_a = 0, it_b = 0, n_done = 0;
       bool alive = true;
+#ifdef WINO_ROW_TRACE
+      // LAP(k): clocks since the previous LAP are charged to segment k (register accumulators, written once)
+      long long lap_t = clock64();
+      unsigned long long lap_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define LAP(k) do { const long long now_ = clock64(); lap_acc[k] += (unsigned long long)(now_ - lap_t); lap_t = now_; } while (0)
+#else
+#define LAP(k) do { } while (0)
+#endif
       const int nbs = sl.n_b_stages;
-      const int slab_bytes = g.slab_rows * 64;
+      const uint32_t slab16 = (uint32_t)(g.slab_rows * 64 / 16);
+      static_assert(KC / UMMA_K == 2, "two K = 16 steps per slab");
       for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x, ++n_done) {
         const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
         const uint32_t use = (ACC_BUFS == 2) ? (n_done >> 1) : n_done;
+        LAP(6);
         if (!mbar_wait(acc_empty(ab), (use & 1u) ^ 1u, abort_word, ERR_MMA_ACC)) { alive = false; break; }
+        LAP(7);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc = tmem_base + (uint32_t)(ab * 4 * BN);
+        const uint32_t acc = tmem_base + (uint32_t)(ab * ACC_COLS);
         bool first = true;
         for (int step = 0; step < steps_per_item && alive; ++step)
           for (int w = 0; w < g.PW && alive; ++w) {
-            const int as = it_a & 1;
-            if (!mbar_wait(a_full(as), (it_a >> 1) & 1u, abort_word, ERR_MMA_A)) { alive = false; break; }
+            const int as = (int)(it_a % (uint32_t)sl.n_a_bufs);
+            if (!((g.dbg & 64u) ? mbar_poll(a_full(as), (it_a / (uint32_t)sl.n_a_bufs) & 1u, abort_word, ERR_MMA_A) : mbar_wait(a_full(as), (it_a / (uint32_t)sl.n_a_bufs) & 1u, abort_word, ERR_MMA_A))) { alive = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_base = base + sl.off_a[as];
+            const uint32_t a_lo0 = desc_lo(base + sl.off_a[as]);
             for (int kh = 0; kh < g.kH; ++kh) {
+              LAP(0);
               const int bs = it_b % nbs;
-              if (!mbar_wait(b_full(bs), (it_b / nbs) & 1u, abort_word, ERR_MMA_B)) { alive = false; break; }
+              if (!((g.dbg & 64u) ? mbar_poll(b_full(bs), (it_b / nbs) & 1u, abort_word, ERR_MMA_B) : mbar_wait(b_full(bs), (it_b / nbs) & 1u, abort_word, ERR_MMA_B))) { alive = false; break; }
+              LAP(1);
               asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-              const uint32_t b_base = base + sl.off_b + bs * sl.b_stage_bytes;
+              const uint32_t b_lo0 = desc_lo(base + sl.off_b + bs * sl.b_stage_bytes);
+              const uint32_t a_lo_kh = a_lo0 + (uint32_t)(kh * g.CBW * 4);      // 64-byte rows = 4 descriptor units
+              const uint32_t acc0 = first ? 0u : 1u;
+              LAP(2);
+              if (!(g.dbg & 8u)) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                // tap kh = the same slab, kh * CBW rows (whole 8-row swizzle groups) further down
-                const uint64_t adesc = make_smem_desc_sw64(a_base + j * slab_bytes + kh * g.CBW * 64);
-                const uint64_t bdesc = make_smem_desc_sw64(b_base + j * (BN * 64));
+                for (int mb = 0; mb < MB; ++mb) {
+                  uint32_t a_lo = a_lo_kh + (uint32_t)(mb * BM * 4);            // block mb starts RB * CBW = 128 rows later
+                  uint32_t b_lo = b_lo0;
 #pragma unroll
-                for (int kk = 0; kk < KC / UMMA_K; ++kk)
-                  umma_f16(acc + (uint32_t)(j * BN), adesc + 2u * kk, bdesc + 2u * kk, idesc, (first && kk == 0) ? 0u : 1u);
+                  for (int j = 0; j < 4; ++j) {
+                    const uint32_t d_col = acc + (uint32_t)((mb * 4 + j) * BN);
+                    umma_f16_lohi(d_col, a_lo, b_lo, idesc, acc0);
+                    umma_f16_lohi(d_col, a_lo + 2u, b_lo + 2u, idesc, 1u);   // second K = 16 step: 32 bytes further
+                    a_lo += slab16;
+                    b_lo += (uint32_t)(BN * 64 / 16);
+                  }
+                }
               }
               first = false;
+              LAP(3);
               umma_commit(b_empty(bs));
+              LAP(4);
               ++it_b;
             }
             umma_commit(a_empty(as));
             ++it_a;
           }
         umma_commit(acc_full(ab));
+        LAP(5);
       }
+#ifdef WINO_ROW_TRACE
+      if (blockIdx.x == 0) for (int k = 0; k < 8; ++k) g_row_trace[16 + k] += lap_acc[k];
+#endif
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -383,12 +474,15 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
       const uint32_t use = (ACC_BUFS == 2) ? (n_done >> 1) : n_done;
       unsigned got = 0;
-      if (lane == 0) got = mbar_wait(acc_full(ab), use & 1u, abort_word, ERR_EPI) ? 1u : 0u;
+      if (lane == 0) got = mbar_wait(acc_full(ab), use & 1u, abort_word, ERR_EPI, (g.dbg & 32u) != 0) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (got == 0u) { alive = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(ab * 4 * BN);
-      const int oh = rb * g.RB + tr, ow = (cb * g.CBW + tcp) * 2;
+      const int ow = (cb * g.CBW + tcp) * 2;
+#pragma unroll 1
+      for (int mb = 0; mb < MB; ++mb) {
+      const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(ab * ACC_COLS + mb * 4 * BN);
+      const int oh = (rb * MB + mb) * g.RB + tr;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t m0[16], m1[16], m2[16], m3[16];
@@ -397,7 +491,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         tmem_ld_x16(t_lane + (uint32_t)(2 * BN + c0), m2);
         tmem_ld_x16(t_lane + (uint32_t)(3 * BN + c0), m3);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 16 >= BN) {   // last columns are in registers: hand the accumulator back
+        if (c0 + 16 >= BN && mb == MB - 1) {   // last columns are in registers: hand the accumulator back
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(acc_empty(ab));
         }
@@ -419,7 +513,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             y0[c] = relu ? fmaxf(mx, 0.f) : mx;
           }
           const int ph = oh >> 1, pw = ow >> 1;
-          if ((tr & 1) == 0 && ph < g.yH && pw < g.yW && kbase < g.K) {
+          if ((tr & 1) == 0 && ph < g.yH && pw < g.yW && kbase < g.K && !(g.dbg & 16u)) {
             T *dst = y + ((((long long)n * g.oD + od) * g.yH + ph) * g.yW + pw) * g.K + kbase;
             store16<T>(dst, y0, kbase, g.K, vec_ok);
           }
@@ -428,17 +522,24 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 #pragma unroll
             for (int c = 0; c < 16; ++c) { y0[c] = fmaxf(y0[c], 0.f); y1[c] = fmaxf(y1[c], 0.f); }
           }
-          if (oh < g.oH && kbase < g.K) {
+          if (oh < g.oH && kbase < g.K && !(g.dbg & 16u)) {
             T *dst = y + ((((long long)n * g.oD + od) * g.oH + oh) * g.oW + ow) * g.K + kbase;
             if (ow < g.oW) store16<T>(dst, y0, kbase, g.K, vec_ok);
             if (ow + 1 < g.oW) store16<T>(dst + g.K, y1, kbase, g.K, vec_ok);
           }
         }
       }
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+#ifdef WINO_ROW_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    g_row_trace[0] += (unsigned long long)(clock64() - trace_kernel_t0);
+    g_row_trace[15] += (unsigned long long)((g.n_items + gridDim.x - 1) / gridDim.x);
+  }
+#endif
   if (warp == 10) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
@@ -516,19 +617,34 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   const int Cp = (d.C + 7) / 8 * 8;
   p.Cp = Cp;
   p.PW = (d.kW + 2) / 3;
-  p.BN = d.K <= 64 ? 64 : 128;
-  // block shape: 8 rows x 16 column pairs or 16 rows x 8 column pairs, whichever wastes fewer tiles
+  // Work item: MB tile blocks stacked along H x BN output channels, MB * BN = 128 (the 512 TMEM columns hold
+  // MB x 4 positions x BN).  Two blocks x 64 channels halve the filter bytes streamed per multiply-add, which is
+  // what the kernel runs out of first; one block x 128 channels is kept for images too short for two blocks.
+  // WINOCONV_ROW_MB=1|2 forces the choice (tuning).
   const int ncp = (d.oW + 1) / 2;
-  auto waste = [&](int rb, int cbw) {
-    const long long blocks = (long long)((d.oH + rb - 1) / rb) * ((ncp + cbw - 1) / cbw);
-    return blocks * 128;
+  auto padded = [&](int rows_item, int cbw) {
+    return (long long)((d.oH + rows_item - 1) / rows_item) * rows_item * ((ncp + cbw - 1) / cbw) * cbw;
   };
-  p.CBW = waste(8, 16) <= waste(16, 8) ? 16 : 8;
+  int best_mb = 0, best_cbw = 0;
+  long long best = -1;
+  static const int forced_mb = [] { const char *v = getenv("WINOCONV_ROW_MB"); return v && *v ? atoi(v) : 0; }();
+  for (int mb = 2; mb >= 1; --mb) {
+    if (forced_mb && mb != forced_mb) continue;
+    for (int cbw : {16, 8}) {
+      const long long vol = padded(mb * (128 / cbw), cbw);
+      // prefer two blocks unless that pads more than 15 % over the best one-block shape
+      const long long score = mb == 2 ? vol * 100 : vol * 115;
+      if (best < 0 || score < best) { best = score; best_mb = mb; best_cbw = cbw; }
+    }
+  }
+  p.MB = best_mb;
+  p.BN = (p.MB == 2 || d.K <= 64) ? 64 : 128;
+  p.CBW = best_cbw;
   p.RB = 128 / p.CBW;
-  p.n_rb = (d.oH + p.RB - 1) / p.RB;
+  p.n_rb = (d.oH + p.MB * p.RB - 1) / (p.MB * p.RB);
   p.n_cb = (ncp + p.CBW - 1) / p.CBW;
-  p.slab_rows = (p.RB + d.kH - 1) * p.CBW;
-  p.patch_h = p.RB + d.kH - 1;
+  p.slab_rows = (p.MB * p.RB + d.kH - 1) * p.CBW;
+  p.patch_h = p.MB * p.RB + d.kH - 1;
   p.patch_w = 2 * p.CBW + 3 * p.PW - 1;
   p.n_chunks = (Cp + KC - 1) / KC;
   p.n_nblocks = (d.K + p.BN - 1) / p.BN;
@@ -536,15 +652,22 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   p.filter_elems = (long long)p.slabs * d.K * Cp;
   p.n_items = (long long)d.N * d.oD * p.n_rb * p.n_cb * p.n_nblocks;
   if (p.patch_w > 256 || p.patch_h > 256) return false;
-  // shared memory: 2 raw patches, 2 slab sets, as many filter stages as fit (2..8)
+  // shared memory: 2 raw patches, 2 slab sets (1 if two do not leave room for 3 filter stages), then as many
+  // filter stages as fit (2..8)
   const int raw_bytes = ((p.patch_h * p.patch_w * KC * 2 + 127) / 128) * 128;
   const int a_bytes = ((4 * p.slab_rows * 64 + 1023) / 1024) * 1024;
   const int b_stage = 4 * p.BN * 64;
-  const int fixed = 2 * raw_bytes + 2 * a_bytes + 1024 /*bars*/ + 1024 /*align*/;
   const int budget = 227 * 1024;
+  int n_a = 2;
+  int fixed = 2 * raw_bytes + n_a * a_bytes + 1024 /*bars*/ + 1024 /*align*/;
+  if ((budget - fixed) / b_stage < 3) {
+    n_a = 1;
+    fixed = 2 * raw_bytes + n_a * a_bytes + 2048;
+  }
   int nb = (budget - fixed) / b_stage;
   if (nb < 2) return false;
   if (nb > 8) nb = 8;
+  p.n_a_bufs = n_a;
   p.raw_bytes = raw_bytes; p.a_bytes = a_bytes; p.b_stage_bytes = b_stage; p.n_b_stages = nb;
   p.smem_total = fixed + nb * b_stage;
   *out = p;
@@ -561,24 +684,27 @@ cudaError_t launch_rowfused_filter_transform(const RowDesc &d, const RowPlan &p,
   return cudaGetLastError();
 }
 
-template <typename T, int BN>
+template <typename T, int BN, int MB>
 static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorMap &mx, const CUtensorMap &mu, void *y,
                              const void *bias, int sm_count, uint32_t idesc, cudaStream_t s, const char **detail) {
   using namespace rowf;
-  auto kern = rowfused_kernel<T, BN>;
+  auto kern = rowfused_kernel<T, BN, MB>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_total);
   if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
   RGeom g;
   g.N = d.N; g.C = d.C; g.K = d.K; g.D = d.D; g.H = d.H; g.W = d.W; g.oD = d.oD; g.oH = d.oH; g.oW = d.oW;
   g.yH = d.yH; g.yW = d.yW; g.pD = d.pD; g.pH = d.pH; g.pW = d.pW; g.kD = d.kD; g.kH = d.kH; g.kW = d.kW;
-  g.PW = p.PW; g.RB = p.RB; g.CBW = p.CBW; g.n_rb = p.n_rb; g.n_cb = p.n_cb; g.slab_rows = p.slab_rows;
+  g.PW = p.PW; g.RB = p.RB; g.CBW = p.CBW; g.MB = p.MB; g.n_rb = p.n_rb; g.n_cb = p.n_cb; g.slab_rows = p.slab_rows;
   g.patch_h = p.patch_h; g.patch_w = p.patch_w; g.n_chunks = p.n_chunks; g.n_nblocks = p.n_nblocks;
   g.n_items = p.n_items; g.epilogue = d.epilogue;
+  static const unsigned dbg = [] { const char *v = getenv("WINOCONV_ROW_DBG"); return v && *v ? (unsigned)atoi(v) : 0u; }();
+  g.dbg = dbg;
   Smem sl;
   sl.raw_bytes = p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
   sl.a_bytes = p.a_bytes; sl.b_stage_bytes = p.b_stage_bytes; sl.n_b_stages = p.n_b_stages;
-  sl.off_a[0] = 0; sl.off_a[1] = p.a_bytes;                       // slabs first: 1024-byte aligned
-  sl.off_b = 2 * p.a_bytes;                                        // filter stages: multiples of 1024
+  sl.n_a_bufs = p.n_a_bufs;
+  sl.off_a[0] = 0; sl.off_a[1] = p.n_a_bufs == 2 ? p.a_bytes : 0;  // slabs first: 1024-byte aligned
+  sl.off_b = p.n_a_bufs * p.a_bytes;                               // filter stages: multiples of 1024
   sl.off_raw[0] = sl.off_b + p.n_b_stages * p.b_stage_bytes;
   sl.off_raw[1] = sl.off_raw[0] + p.raw_bytes;
   sl.off_bars = sl.off_raw[1] + p.raw_bytes;
@@ -638,12 +764,27 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   if (e != cudaSuccess) { *detail = "cudaDeviceGetAttribute(MultiProcessorCount) failed"; return e; }
   const uint32_t fmt = dtype == WINOCONV_F16 ? 0u : 1u;
   const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-  if (dtype == WINOCONV_F16)
-    return p.BN == 64 ? launch_rf<__half, 64>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)
-                      : launch_rf<__half, 128>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
-  return p.BN == 64 ? launch_rf<__nv_bfloat16, 64>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)
-                    : launch_rf<__nv_bfloat16, 128>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
+  if (dtype == WINOCONV_F16) {
+    if (p.MB == 2) return launch_rf<__half, 64, 2>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
+    return p.BN == 64 ? launch_rf<__half, 64, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)
+                      : launch_rf<__half, 128, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
+  }
+  if (p.MB == 2) return launch_rf<__nv_bfloat16, 64, 2>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
+  return p.BN == 64 ? launch_rf<__nv_bfloat16, 64, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)
+                    : launch_rf<__nv_bfloat16, 128, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
 }
+
+#ifdef WINO_ROW_TRACE
+extern "C" __attribute__((visibility("default"))) int winoconv_debug_row_trace(unsigned long long *out, int clear) {
+  cudaDeviceSynchronize();
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_row_trace, sizeof(unsigned long long) * 32);
+  if (e == cudaSuccess && clear) {
+    unsigned long long z[32] = {};
+    e = cudaMemcpyToSymbol(g_row_trace, z, sizeof(z));
+  }
+  return (int)e;
+}
+#endif
 
 cudaError_t read_and_clear_row_error(cudaStream_t s, unsigned int *code) {
   unsigned int host = 0, zero = 0;
