@@ -41,7 +41,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
 # summarised under profiles/ (None until a capture exists for that kernel and workload).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {
+    # rowfused_kernel, C = K = 256 at 56 x 56 (VGG layers 6-7): 365.5 MB at N = 128 in the capture of
+    # profiles/rowfused_c256_k256_56_ncu.md, scaled to the bench's N = 256 (traffic is proportional to N)
+    ("vgg16", "rowfused_kernel"): 731.0e6,
+}
 
 
 def load_peaks():
@@ -319,18 +323,42 @@ def run_ours(args):
     value = total_images * args.steps / (ms / 1e3)
 
     # ---- region 2: end to end from pinned host memory ---------------------------------------------
-    def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        y = model.replay(x_dev) if use_graph else model(x_dev)
-        y_host.copy_(y, non_blocking=True)
+    # Every step copies its batch host -> device and its result device -> host.  The copies run on their own
+    # stream into two alternating input buffers, so the H2D copy of step i+1 overlaps the kernels of step i;
+    # all copies of the K timed steps lie between the two events.
+    main = torch.cuda.current_stream(dev)
+    copy_stream = torch.cuda.Stream(device=dev)
+    x_bufs = [x_dev, torch.empty_like(x_dev)]
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
 
-    for _ in range(3):
-        e2e_step()
+    def issue_copy(i):
+        b = i % 2
+        copy_stream.wait_event(consumed[b])
+        with torch.cuda.stream(copy_stream):
+            x_bufs[b].copy_(x_host, non_blocking=True)
+            copied[b].record(copy_stream)
+
+    def run_e2e(n_steps):
+        for b in range(2):
+            consumed[b].record(main)
+        copy_stream.wait_stream(main)
+        issue_copy(0)
+        for i in range(n_steps):
+            b = i % 2
+            if i + 1 < n_steps:
+                issue_copy(i + 1)
+            main.wait_event(copied[b])
+            y = model.forward(x_bufs[b])
+            consumed[b].record(main)
+            y_host.copy_(y, non_blocking=True)
+        main.wait_stream(copy_stream)
+
+    run_e2e(3)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    run_e2e(args.steps)
     f1.record()
     barrier()
     ms_e2e = sharding.max_over_ranks(f0.elapsed_time(f1))

@@ -38,6 +38,10 @@ __device__ unsigned int g_row_error = 0;
 #ifdef WINO_ROW_TRACE
 // Development aid (not built by default): per-role accumulated wait clocks of CTA 0.
 __device__ unsigned long long g_row_trace[32];
+__device__ unsigned long long g_row_tl[10][256];     // event timeline of CTA 0: [role][event index] = clock64
+#define TL(role, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_row_tl[role][idx] = (unsigned long long)clock64(); } while (0)
+#else
+#define TL(role, idx) do { } while (0)
 #endif
 
 namespace rowf {
@@ -216,6 +220,7 @@ struct Smem {
 
 struct RGeom {
   int N, C, K;
+  int Cp;                 // channels of the (padded) input the TMA map addresses
   int D, H, W, oD, oH, oW, yH, yW;
   int pD, pH, pW, kD, kH, kW;
   int PW;                 // F(2,3) windows along W: ceil(kW / 3)
@@ -294,6 +299,11 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     n = (int)item;
   };
   const int steps_per_item = g.kD * g.n_chunks;          // raw patches per item
+  // CTAs walk the channel slabs in rotated order so that they do not all ask L2 for the same filter slab at once
+  const int rot = (g.dbg & 256u) ? 0 : (int)(blockIdx.x % (unsigned)g.n_chunks);
+  // When one channel block covers K and a whole item's filter slabs fit the stage ring, they are loaded once and
+  // stay: stage index = slab position within the item, no refills.
+  const bool b_resident = g.n_nblocks == 1 && steps_per_item * g.PW * g.kH <= sl.n_b_stages && !(g.dbg & 512u);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- raw input patches
@@ -309,7 +319,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             if (!mbar_wait(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY, (g.dbg & 32u) != 0)) { alive = false; break; }
             if (g.dbg & 2u) { mbar_arrive(raw_full(s)); ++it; continue; }
             mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
-            tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
+            tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ((ch + rot) % g.n_chunks) * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
                         od + kd - g.pD, n);
             ++it;
           }
@@ -325,11 +335,13 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x) {
       for (int step = 0; step < steps_per_item && alive; ++step) {
         const int rs = it_raw & 1;
-        if (!mbar_wait(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW, (g.dbg & 32u) != 0)) { alive = false; break; }
+        if (!((g.dbg & 128u) ? mbar_poll(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW) : mbar_wait(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW, (g.dbg & 32u) != 0))) { alive = false; break; }
+        if (ptid == 0) TL(8, it_raw);
         const uint8_t *raw = base_ptr + sl.off_raw[rs];
         for (int w = 0; w < g.PW && alive; ++w) {
           const int as = (int)(it_a % (uint32_t)sl.n_a_bufs);
-          if (!mbar_wait(a_empty(as), ((it_a / (uint32_t)sl.n_a_bufs) & 1u) ^ 1u, abort_word, ERR_PROD_A, (g.dbg & 32u) != 0)) { alive = false; break; }
+          if (!((g.dbg & 128u) ? mbar_poll(a_empty(as), ((it_a / (uint32_t)sl.n_a_bufs) & 1u) ^ 1u, abort_word, ERR_PROD_A) : mbar_wait(a_empty(as), ((it_a / (uint32_t)sl.n_a_bufs) & 1u) ^ 1u, abort_word, ERR_PROD_A, (g.dbg & 32u) != 0))) { alive = false; break; }
+          if (ptid == 0) TL(4, it_a);
           uint8_t *slab = base_ptr + sl.off_a[as];
           const int slab_bytes = g.slab_rows * 64;
           for (int row = ptid >> 2; row < ((g.dbg & 4u) ? 0 : n_tasks); row += N_PROD / 4) {
@@ -350,6 +362,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           mbar_arrive(a_full(as));
+          if (ptid == 0) TL(5, it_a);
           ++it_a;
         }
         if (alive) mbar_arrive(raw_empty(rs));     // all windows of this patch are transformed
@@ -365,18 +378,21 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x) {
         int n, od, rb, cb, nb;
         decode(item, n, od, rb, cb, nb);
+        if (b_resident && item != (long long)blockIdx.x) break;   // every slab of the filter is already in shared memory
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks && alive; ++ch)
             for (int w = 0; w < g.PW && alive; ++w)
               for (int kh = 0; kh < g.kH; ++kh) {
                 const int s = it % nbs;
                 if (!((g.dbg & 64u) ? mbar_poll(b_empty(s), ((it / nbs) & 1u) ^ 1u, abort_word, ERR_B_EMPTY) : mbar_wait(b_empty(s), ((it / nbs) & 1u) ^ 1u, abort_word, ERR_B_EMPTY, (g.dbg & 32u) != 0))) { alive = false; break; }
+                TL(2, it);
                 if (g.dbg & 1u) { mbar_arrive(b_full(s)); ++it; continue; }
                 mbar_expect_tx(b_full(s), (uint32_t)sl.b_stage_bytes);
                 const int slab0 = ((kd * g.kH + kh) * g.PW + w) * 4;
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                  tma_load_3d(base + sl.off_b + s * sl.b_stage_bytes + j * (BN * 64), &map_u, b_full(s), ch * KC, nb * BN, slab0 + j);
+                  tma_load_3d(base + sl.off_b + s * sl.b_stage_bytes + j * (BN * 64), &map_u, b_full(s), ((ch + rot) % g.n_chunks) * KC, nb * BN, slab0 + j);
+                TL(3, it);
                 ++it;
               }
       }
@@ -388,6 +404,25 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   } else if (warp == 10) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
+#ifdef WINO_ROW_TRACE
+      if (blockIdx.x == 0) {   // latency of an empty tcgen05.commit -> mbarrier flip, and of a plain arrive
+        const uint32_t tb = bars + 8u * 28;
+        mbar_init(tb, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int rep = 0; rep < 4; ++rep) {
+          const long long t0 = clock64();
+          umma_commit(tb);
+          while (!mbar_test_wait(tb, (uint32_t)(rep & 1))) { }
+          g_row_trace[24] += (unsigned long long)(clock64() - t0);
+        }
+        for (int rep = 4; rep < 8; ++rep) {
+          const long long t0 = clock64();
+          mbar_arrive(tb);
+          while (!mbar_test_wait(tb, (uint32_t)(rep & 1))) { }
+          g_row_trace[25] += (unsigned long long)(clock64() - t0);
+        }
+      }
+#endif
       uint32_t it_a = 0, it_b = 0, n_done = 0;
       bool alive = true;
 #ifdef WINO_ROW_TRACE
@@ -410,17 +445,21 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem_base + (uint32_t)(ab * ACC_COLS);
         bool first = true;
-        for (int step = 0; step < steps_per_item && alive; ++step)
+        for (int step = 0; step < steps_per_item && alive; ++step) {
+          // a slab with at most 16 real channels (few-channel input, or the tail of C) needs one K = 16 step only
+          const bool k2 = g.Cp - ((step + rot) % g.n_chunks) * KC > UMMA_K;
           for (int w = 0; w < g.PW && alive; ++w) {
             const int as = (int)(it_a % (uint32_t)sl.n_a_bufs);
             if (!((g.dbg & 64u) ? mbar_poll(a_full(as), (it_a / (uint32_t)sl.n_a_bufs) & 1u, abort_word, ERR_MMA_A) : mbar_wait(a_full(as), (it_a / (uint32_t)sl.n_a_bufs) & 1u, abort_word, ERR_MMA_A))) { alive = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TL(9, it_a);
             const uint32_t a_lo0 = desc_lo(base + sl.off_a[as]);
             for (int kh = 0; kh < g.kH; ++kh) {
               LAP(0);
-              const int bs = it_b % nbs;
-              if (!((g.dbg & 64u) ? mbar_poll(b_full(bs), (it_b / nbs) & 1u, abort_word, ERR_MMA_B) : mbar_wait(b_full(bs), (it_b / nbs) & 1u, abort_word, ERR_MMA_B))) { alive = false; break; }
-              LAP(1);
+              const int bs = b_resident ? (int)(it_b % (uint32_t)(steps_per_item * g.PW * g.kH)) : (int)(it_b % nbs);
+              if (!(b_resident && n_done > 0))
+                if (!((g.dbg & 64u) ? mbar_poll(b_full(bs), b_resident ? 0u : ((it_b / nbs) & 1u), abort_word, ERR_MMA_B) : mbar_wait(b_full(bs), b_resident ? 0u : ((it_b / nbs) & 1u), abort_word, ERR_MMA_B))) { alive = false; break; }
+              LAP(1); TL(0, it_b);
               asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
               const uint32_t b_lo0 = desc_lo(base + sl.off_b + bs * sl.b_stage_bytes);
               const uint32_t a_lo_kh = a_lo0 + (uint32_t)(kh * g.CBW * 4);      // 64-byte rows = 4 descriptor units
@@ -435,21 +474,22 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
                   for (int j = 0; j < 4; ++j) {
                     const uint32_t d_col = acc + (uint32_t)((mb * 4 + j) * BN);
                     umma_f16_lohi(d_col, a_lo, b_lo, idesc, acc0);
-                    umma_f16_lohi(d_col, a_lo + 2u, b_lo + 2u, idesc, 1u);   // second K = 16 step: 32 bytes further
+                    if (k2) umma_f16_lohi(d_col, a_lo + 2u, b_lo + 2u, idesc, 1u);   // second K = 16 step: 32 bytes further
                     a_lo += slab16;
                     b_lo += (uint32_t)(BN * 64 / 16);
                   }
                 }
               }
               first = false;
-              LAP(3);
-              umma_commit(b_empty(bs));
+              LAP(3); TL(1, it_b);
+              if (!b_resident) umma_commit(b_empty(bs));
               LAP(4);
               ++it_b;
             }
             umma_commit(a_empty(as));
             ++it_a;
           }
+        }
         umma_commit(acc_full(ab));
         LAP(5);
       }
@@ -477,6 +517,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       if (lane == 0) got = mbar_wait(acc_full(ab), use & 1u, abort_word, ERR_EPI, (g.dbg & 32u) != 0) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (got == 0u) { alive = false; break; }
+      if (warp == 11 && lane == 0) TL(6, n_done);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int ow = (cb * g.CBW + tcp) * 2;
 #pragma unroll 1
@@ -494,6 +535,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         if (c0 + 16 >= BN && mb == MB - 1) {   // last columns are in registers: hand the accumulator back
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(acc_empty(ab));
+          if (warp == 11 && lane == 0) TL(7, n_done);
         }
         const int kbase = nb * BN + c0;
         float y0[16], y1[16];
@@ -577,15 +619,20 @@ __global__ void __launch_bounds__(256) rowfused_filter_kernel(const T *__restric
   for (int j = 0; j < 4; ++j) Elem<T>::store(u + ((slab0 + j) * K + k) * Cp + c, o[j]);
 }
 
-// zero-pads the channel dimension to a multiple of 8 so the input can be addressed by TMA
+// zero-pads the channel dimension to a multiple of 8 so the input can be addressed by TMA; one thread writes one
+// 16-byte group of eight channels
 template <typename T>
 __global__ void __launch_bounds__(256) pad_channels_kernel(const T *__restrict__ x, T *__restrict__ xp, long long pixels,
                                                            int C, int Cp) {
+  const int groups = Cp / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= pixels * Cp) return;
-  const long long px = idx / Cp;
-  const int c = (int)(idx - px * Cp);
-  xp[idx] = c < C ? x[px * C + c] : T(0.f);
+  if (idx >= pixels * groups) return;
+  const long long px = idx / groups;
+  const int c0 = (int)(idx - px * groups) * 8;
+  __align__(16) T v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = (c0 + i < C) ? x[px * C + c0 + i] : T(0.f);
+  *reinterpret_cast<uint4 *>(xp + px * Cp + c0) = *reinterpret_cast<const uint4 *>(v);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -692,7 +739,7 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_total);
   if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
   RGeom g;
-  g.N = d.N; g.C = d.C; g.K = d.K; g.D = d.D; g.H = d.H; g.W = d.W; g.oD = d.oD; g.oH = d.oH; g.oW = d.oW;
+  g.N = d.N; g.C = d.C; g.K = d.K; g.Cp = p.Cp; g.D = d.D; g.H = d.H; g.W = d.W; g.oD = d.oD; g.oH = d.oH; g.oW = d.oW;
   g.yH = d.yH; g.yW = d.yW; g.pD = d.pD; g.pH = d.pH; g.pW = d.pW; g.kD = d.kD; g.kH = d.kH; g.kW = d.kW;
   g.PW = p.PW; g.RB = p.RB; g.CBW = p.CBW; g.MB = p.MB; g.n_rb = p.n_rb; g.n_cb = p.n_cb; g.slab_rows = p.slab_rows;
   g.patch_h = p.patch_h; g.patch_w = p.patch_w; g.n_chunks = p.n_chunks; g.n_nblocks = p.n_nblocks;
@@ -724,7 +771,7 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   if (p.Cp != d.C) {   // channels not a multiple of 8: TMA needs 16-byte pixel strides, so pad into scratch first
     if (!pad_ws) { *detail = "channel padding scratch missing"; return cudaErrorInvalidValue; }
     const long long pixels = (long long)d.N * d.D * d.H * d.W;
-    const unsigned blocks = (unsigned)((pixels * p.Cp + 255) / 256);
+    const unsigned blocks = (unsigned)((pixels * (p.Cp / 8) + 255) / 256);
     if (dtype == WINOCONV_F16)
       pad_channels_kernel<__half><<<blocks, 256, 0, s>>>((const __half *)x, (__half *)pad_ws, pixels, d.C, p.Cp);
     else
@@ -775,6 +822,10 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
 }
 
 #ifdef WINO_ROW_TRACE
+extern "C" __attribute__((visibility("default"))) int winoconv_debug_row_timeline(unsigned long long *out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, g_row_tl, sizeof(unsigned long long) * 10 * 256);
+}
 extern "C" __attribute__((visibility("default"))) int winoconv_debug_row_trace(unsigned long long *out, int clear) {
   cudaDeviceSynchronize();
   cudaError_t e = cudaMemcpyFromSymbol(out, g_row_trace, sizeof(unsigned long long) * 32);
