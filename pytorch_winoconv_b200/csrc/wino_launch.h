@@ -42,6 +42,7 @@ struct RowPlan {
   int Cp, PW, BN, MB, CBW, RB, n_rb, n_cb, slab_rows, patch_h, patch_w, n_chunks, n_nblocks, slabs;
   long long filter_elems, n_items;
   int raw_bytes, a_bytes, b_stage_bytes, n_b_stages, n_a_bufs, smem_total;
+  int pair;   // 1: CTA pairs (two images per work item, one M = 256 MMA over both SMs, filter slabs split between them)
 };
 bool rowfused_plan(const RowDesc &d, RowPlan *out);
 cudaError_t launch_rowfused_filter_transform(const RowDesc &d, const RowPlan &p, int dtype, const void *w, void *u, cudaStream_t s);

@@ -16,9 +16,11 @@
 //   warp 0       TMA: raw input patch (5-D box, zero fill = padding) per 32-channel slab
 //   warps 1-8    F(2,3) along W on the patch: raw -> four [rows x 32] slabs, 64-byte swizzle, fence.proxy.async
 //   warp 9       TMA: transformed-filter slabs of the current (kd, kh, window), four positions per stage
-//   warp 10      tcgen05.mma (M = 128, N = BN, K = 16) issue + commits; TMEM alloc
-//   warps 11-14  epilogue: tcgen05.ld, A^T along W, bias / ReLU / 2x2 max-pool (row partner by shuffle), 32-byte stores
+//   warps 10-11  tcgen05.mma (M = 128, N = BN, K = 16) issue + commits, two positions each; warp 10: TMEM alloc
+//   warps 12-15  epilogue: tcgen05.ld, A^T along W, bias / ReLU / 2x2 max-pool (row partner by shuffle), 32-byte stores
 // V and M never exist in global memory.  Every mbarrier wait is bounded and reports through the error word.
+// With a batch of two or more and streamed filter slabs the CTAs run as pairs (clusters of two, cta_group::2):
+// one M = 256 MMA covers the tile blocks of both, and each loads only its half of every filter slab.
 //
 // Reference counterparts: the whole chain of src/base_conv_launchers.cu:338-381 (inputNorm2WinoTransform,
 // cublas batched GEMM, outputWino2NormTransform, outputAggregate) and the piece table of
@@ -39,7 +41,11 @@ __device__ unsigned int g_row_error = 0;
 // Development aid (not built by default): per-role accumulated wait clocks of CTA 0.
 __device__ unsigned long long g_row_trace[32];
 __device__ unsigned long long g_row_tl[10][256];     // event timeline of CTA 0: [role][event index] = clock64
+#ifdef WINO_ROW_TL
 #define TL(role, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_row_tl[role][idx] = (unsigned long long)clock64(); } while (0)
+#else
+#define TL(role, idx) do { } while (0)
+#endif
 #else
 #define TL(role, idx) do { } while (0)
 #endif
@@ -50,7 +56,8 @@ constexpr int BM = 128;            // tiles per block == TMEM lanes
 constexpr int KC = 32;             // reduction slab (channels): 64-byte rows
 constexpr int UMMA_K = 16;
 constexpr int N_PROD = 256;
-constexpr int N_THREADS = 480;     // 15 warps
+constexpr int N_THREADS = 512;     // 16 warps
+constexpr int N_MMA_THREADS = 2;   // MMA issuers: thread h takes positions 2h and 2h + 1 of every stage
 constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;
 
 enum ErrCode : unsigned {
@@ -77,6 +84,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok;
 }
+#ifdef WINO_ROW_TRACE
 __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -86,32 +94,11 @@ __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok;
 }
-// Polling wait (non-blocking test_wait) for the two threads on the MMA critical path.
-__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long start = clock64();
-  unsigned spins = 0;
-  while (!mbar_test_wait(bar, parity)) {
-    if ((++spins & 63u) == 0u) {
-      if (*abort_word != 0u) return false;
-      if (clock64() - start > WAIT_LIMIT_CLOCKS) {
-        *abort_word = code;
-        atomicCAS(&g_row_error, 0u, code);
-        return false;
-      }
-    }
-  }
-#ifdef WINO_ROW_TRACE
-  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_row_trace[code & 15u], (unsigned long long)(clock64() - start));
 #endif
-  return true;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code,
-                                          bool backoff = false) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (backoff) __nanosleep(200);     // roles with slack yield their issue slots to the MMA thread
     if (*abort_word != 0u) return false;
     if (clock64() - start > WAIT_LIMIT_CLOCKS) {
       *abort_word = code;
@@ -162,6 +149,66 @@ __device__ __forceinline__ void umma_f16_lohi(uint32_t tmem_d, uint32_t a_lo, ui
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// ---- CTA pairs (cluster of two, tcgen05 cta_group::2): one MMA spans both SMs (M = 256: 128 tiles from each), each
+// SM loads only its half of every filter slab, so the filter bytes an SM pulls from L2 per multiply-add halve.
+// The even CTA of the pair (rank 0) issues the MMAs; barriers it waits on collect arrivals from both CTAs.
+// Shared-memory addresses of a cluster carry the CTA rank in bit 24: clearing it names the same offset in rank 0.
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_rank0(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PEER_BIT_MASK) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// wait with cluster-scope acquire (arrivals come from the peer CTA too)
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (*abort_word != 0u) return false;
+    if (clock64() - start > WAIT_LIMIT_CLOCKS) {
+      *abort_word = code;
+      atomicCAS(&g_row_error, 0u, code);
+      return false;
+    }
+  }
+  return true;
+}
+// filter slab load of a pair: both CTAs issue it for their own half; the bytes are counted on rank 0's barrier
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & PEER_BIT_MASK), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void umma_f16_lohi_pair(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_HI_SW64), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this offset in both CTAs once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -236,7 +283,7 @@ struct RGeom {
   unsigned dbg;           // timing experiments only (WINOCONV_ROW_DBG): 1 no filter TMA, 2 no input TMA, 4 no transform, 8 no MMA, 16 no stores
 };
 
-template <typename T, int BN, int MB>
+template <typename T, int BN, int MB, bool PAIR>
 __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                  const __grid_constant__ CUtensorMap map_u,
                                                                  T *__restrict__ y, const T *__restrict__ bias,
@@ -268,27 +315,41 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(raw_full(i), 1);
-      mbar_init(raw_empty(i), N_PROD);
-      mbar_init(a_full(i), N_PROD);
-      mbar_init(a_empty(i), 1);
-      mbar_init(acc_full(i), 1);
-      mbar_init(acc_empty(i), 128);
+      mbar_init(raw_empty(i), N_PROD / 32);                      // one arrival per producer warp
+      mbar_init(a_full(i), PAIR ? 2 * (N_PROD / 32) : N_PROD / 32);
+      mbar_init(a_empty(i), N_MMA_THREADS);                      // one commit per MMA-issuing thread
+      mbar_init(acc_full(i), N_MMA_THREADS);
+      mbar_init(acc_empty(i), PAIR ? 8 : 4);                     // one arrival per epilogue warp
     }
     for (int i = 0; i < 8; ++i) {
       mbar_init(b_full(i), 1);
-      mbar_init(b_empty(i), 1);
+      mbar_init(b_empty(i), N_MMA_THREADS);
     }
     *abort_word = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  if (PAIR) {   // barriers of both CTAs exist before either allocates or arrives remotely
+    __syncthreads();
+    cluster_sync_all();
+  }
   if (warp == 10) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // work items of this CTA (of this pair): the two CTAs of a pair take images 2n and 2n + 1 of the same item
+  const long long item0 = PAIR ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
+  const long long item_step = PAIR ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
 
   // item -> (n, od, rb, cb, nb); the channel block is the fastest index so consecutive CTAs share a patch
   auto decode = [&](long long item, int &n, int &od, int &rb, int &cb, int &nb) {
@@ -296,30 +357,28 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     cb = (int)(item % g.n_cb); item /= g.n_cb;
     rb = (int)(item % g.n_rb); item /= g.n_rb;
     od = (int)(item % g.oD); item /= g.oD;
-    n = (int)item;
+    n = PAIR ? 2 * (int)item + (int)rank : (int)item;
   };
   const int steps_per_item = g.kD * g.n_chunks;          // raw patches per item
-  // CTAs walk the channel slabs in rotated order so that they do not all ask L2 for the same filter slab at once
-  const int rot = (g.dbg & 256u) ? 0 : (int)(blockIdx.x % (unsigned)g.n_chunks);
   // When one channel block covers K and a whole item's filter slabs fit the stage ring, they are loaded once and
   // stay: stage index = slab position within the item, no refills.
-  const bool b_resident = g.n_nblocks == 1 && steps_per_item * g.PW * g.kH <= sl.n_b_stages && !(g.dbg & 512u);
+  const bool b_resident = !PAIR && g.n_nblocks == 1 && steps_per_item * g.PW * g.kH <= sl.n_b_stages;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- raw input patches
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
-      for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x) {
+      for (long long item = item0; item < g.n_items && alive; item += item_step) {
         int n, od, rb, cb, nb;
         decode(item, n, od, rb, cb, nb);
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks; ++ch) {
             const int s = it & 1;
-            if (!mbar_wait(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY, (g.dbg & 32u) != 0)) { alive = false; break; }
+            if (!mbar_wait(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
             if (g.dbg & 2u) { mbar_arrive(raw_full(s)); ++it; continue; }
             mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
-            tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ((ch + rot) % g.n_chunks) * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
+            tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
                         od + kd - g.pD, n);
             ++it;
           }
@@ -331,21 +390,30 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     const int v = ptid & 3;                            // 16-byte vector of the 32-channel slab
     const int n_tasks = g.slab_rows;                   // one task = one slab row (input row, column pair) x one vector
     uint32_t it_raw = 0, it_a = 0;
+    int as = 0;
+    uint32_t a_par = 1u;                               // parity of the "slab set is free" wait: first round passes
+    const int cbw_shift = g.CBW == 16 ? 4 : 3;         // CBW is 16 or 8
     bool alive = true;
-    for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x) {
+    for (long long item = item0; item < g.n_items && alive; item += item_step) {
       for (int step = 0; step < steps_per_item && alive; ++step) {
         const int rs = it_raw & 1;
-        if (!((g.dbg & 128u) ? mbar_poll(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW) : mbar_wait(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW, (g.dbg & 32u) != 0))) { alive = false; break; }
+        // lane 0 polls, the warp follows: the outcome is uniform, so the warp stays converged for the elected arrivals
+        unsigned ok = 0;
+        if (lane == 0) ok = mbar_wait(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW) ? 1u : 0u;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok == 0u) { alive = false; break; }
         if (ptid == 0) TL(8, it_raw);
         const uint8_t *raw = base_ptr + sl.off_raw[rs];
         for (int w = 0; w < g.PW && alive; ++w) {
-          const int as = (int)(it_a % (uint32_t)sl.n_a_bufs);
-          if (!((g.dbg & 128u) ? mbar_poll(a_empty(as), ((it_a / (uint32_t)sl.n_a_bufs) & 1u) ^ 1u, abort_word, ERR_PROD_A) : mbar_wait(a_empty(as), ((it_a / (uint32_t)sl.n_a_bufs) & 1u) ^ 1u, abort_word, ERR_PROD_A, (g.dbg & 32u) != 0))) { alive = false; break; }
+          ok = 0;
+          if (lane == 0) ok = mbar_wait(a_empty(as), a_par, abort_word, ERR_PROD_A) ? 1u : 0u;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (ok == 0u) { alive = false; break; }
           if (ptid == 0) TL(4, it_a);
           uint8_t *slab = base_ptr + sl.off_a[as];
           const int slab_bytes = g.slab_rows * 64;
           for (int row = ptid >> 2; row < ((g.dbg & 4u) ? 0 : n_tasks); row += N_PROD / 4) {
-            const int ir = row / g.CBW, cp = row - ir * g.CBW;
+            const int ir = row >> cbw_shift, cp = row - (ir << cbw_shift);
             const uint8_t *src = raw + ((size_t)(ir * g.patch_w + 2 * cp + 3 * w) * KC + v * 8) * 2;
             V8<T> d0, d1, d2, d3;
             *reinterpret_cast<uint4 *>(&d0) = *reinterpret_cast<const uint4 *>(src);
@@ -360,12 +428,15 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             *reinterpret_cast<uint4 *>(slab + 2 * slab_bytes + off) = *reinterpret_cast<const uint4 *>(&o2);
             *reinterpret_cast<uint4 *>(slab + 3 * slab_bytes + off) = *reinterpret_cast<const uint4 *>(&o3);
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive(a_full(as));
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // each writer: its stores before the MMA's reads
+          __syncwarp();
+          if (lane == 0) { if (PAIR) mbar_arrive_rank0(a_full(as)); else mbar_arrive(a_full(as)); }
           if (ptid == 0) TL(5, it_a);
           ++it_a;
+          if (++as == sl.n_a_bufs) { as = 0; a_par ^= 1u; }
         }
-        if (alive) mbar_arrive(raw_empty(rs));     // all windows of this patch are transformed
+        __syncwarp();
+        if (alive && lane == 0) mbar_arrive(raw_empty(rs));     // all windows of this patch are transformed
         ++it_raw;
       }
     }
@@ -375,25 +446,36 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       uint32_t it = 0;
       bool alive = true;
       const int nbs = sl.n_b_stages;
-      for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x) {
+      int s = 0;
+      uint32_t s_par = 1u;                          // parity of the "stage is free" wait: first round passes
+      uint32_t dst = base + sl.off_b;
+      for (long long item = item0; item < g.n_items && alive; item += item_step) {
         int n, od, rb, cb, nb;
         decode(item, n, od, rb, cb, nb);
-        if (b_resident && item != (long long)blockIdx.x) break;   // every slab of the filter is already in shared memory
+        if (b_resident && item != item0) break;   // every slab of the filter is already in shared memory
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks && alive; ++ch)
             for (int w = 0; w < g.PW && alive; ++w)
               for (int kh = 0; kh < g.kH; ++kh) {
-                const int s = it % nbs;
-                if (!((g.dbg & 64u) ? mbar_poll(b_empty(s), ((it / nbs) & 1u) ^ 1u, abort_word, ERR_B_EMPTY) : mbar_wait(b_empty(s), ((it / nbs) & 1u) ^ 1u, abort_word, ERR_B_EMPTY, (g.dbg & 32u) != 0))) { alive = false; break; }
+                if (!mbar_wait(b_empty(s), s_par, abort_word, ERR_B_EMPTY)) { alive = false; break; }
                 TL(2, it);
-                if (g.dbg & 1u) { mbar_arrive(b_full(s)); ++it; continue; }
-                mbar_expect_tx(b_full(s), (uint32_t)sl.b_stage_bytes);
                 const int slab0 = ((kd * g.kH + kh) * g.PW + w) * 4;
+                if (PAIR) {   // this CTA's half (BN / 2 rows) of each slab; rank 0 expects the bytes of both halves
+                  if (rank == 0) mbar_expect_tx(b_full(s), 2u * (uint32_t)sl.b_stage_bytes);
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  tma_load_3d(base + sl.off_b + s * sl.b_stage_bytes + j * (BN * 64), &map_u, b_full(s), ((ch + rot) % g.n_chunks) * KC, nb * BN, slab0 + j);
+                  for (int j = 0; j < 4; ++j)
+                    tma_load_3d_pair(dst + j * (BN / 2 * 64), &map_u, b_full(s), ch * KC,
+                                     nb * BN + (int)rank * (BN / 2), slab0 + j);
+                } else {
+                  mbar_expect_tx(b_full(s), (uint32_t)sl.b_stage_bytes);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    tma_load_3d(dst + j * (BN * 64), &map_u, b_full(s), ch * KC, nb * BN, slab0 + j);
+                }
                 TL(3, it);
                 ++it;
+                dst += (uint32_t)sl.b_stage_bytes;
+                if (++s == nbs) { s = 0; s_par ^= 1u; dst = base + sl.off_b; }
               }
       }
       if (*abort_word != 0u) {
@@ -401,100 +483,107 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         while (clock64() - start < 2000000LL) { }
       }
     }
-  } else if (warp == 10) {
-    // ---------------------------------------------------------------- MMA issue
-    if (lane == 0) {
-#ifdef WINO_ROW_TRACE
-      if (blockIdx.x == 0) {   // latency of an empty tcgen05.commit -> mbarrier flip, and of a plain arrive
-        const uint32_t tb = bars + 8u * 28;
-        mbar_init(tb, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int rep = 0; rep < 4; ++rep) {
-          const long long t0 = clock64();
-          umma_commit(tb);
-          while (!mbar_test_wait(tb, (uint32_t)(rep & 1))) { }
-          g_row_trace[24] += (unsigned long long)(clock64() - t0);
-        }
-        for (int rep = 4; rep < 8; ++rep) {
-          const long long t0 = clock64();
-          mbar_arrive(tb);
-          while (!mbar_test_wait(tb, (uint32_t)(rep & 1))) { }
-          g_row_trace[25] += (unsigned long long)(clock64() - t0);
-        }
-      }
-#endif
+  } else if (warp == 10 || warp == 11) {
+    // ---------------------------------------------------------------- MMA issue (rank 0 of a pair issues for both CTAs)
+    // Issuing one tcgen05.mma costs the thread about as long as an N = 128 MMA runs (~60 clocks), so whatever else
+    // a single issuer does (barrier waits, commits, loop branches) is time the tensor pipe idles.  Two threads in
+    // two warps each issue half of every stage (their own two of the four positions, i.e. their own accumulator
+    // columns); while one waits or commits the other keeps the pipe fed.
+    const int half = warp - 10;
+    if (lane == 0 && rank == 0) {
+#define MMA_WAIT(bar_, par_, aw_, code_) mbar_wait(bar_, par_, aw_, code_)
+#define MMA_ISSUE(d_, a_, b_, i_, acc_) do { if (PAIR) umma_f16_lohi_pair(d_, a_, b_, i_, acc_); else umma_f16_lohi(d_, a_, b_, i_, acc_); } while (0)
+#define MMA_COMMIT(bar_) do { if (PAIR) umma_commit_pair(bar_); else umma_commit(bar_); } while (0)
       uint32_t it_a = 0, it_b = 0, n_done = 0;
       bool alive = true;
 #ifdef WINO_ROW_TRACE
       // LAP(k): clocks since the previous LAP are charged to segment k (register accumulators, written once)
-      long long lap_t = clock64();
-      unsigned long long lap_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#define LAP(k) do { const long long now_ = clock64(); lap_acc[k] += (unsigned long long)(now_ - lap_t); lap_t = now_; } while (0)
+      unsigned lap_t = (unsigned)clock();
+      unsigned lap_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#define LAP(k) do { if (half == 0) { const unsigned now_ = (unsigned)clock(); lap_acc[k] += now_ - lap_t; lap_t = now_; } } while (0)
 #else
 #define LAP(k) do { } while (0)
 #endif
-      const int nbs = sl.n_b_stages;
+      // Everything the loop needs per stage is kept incrementally (ring position, parity, descriptor, barrier address):
+      // this one thread feeds the tensor pipe, and a division or a descriptor rebuild per stage shows up as idle MMA time.
       const uint32_t slab16 = (uint32_t)(g.slab_rows * 64 / 16);
+      constexpr uint32_t B_SLAB16 = (uint32_t)((PAIR ? BN / 2 : BN) * 64 / 16);   // a CTA of a pair holds half the rows
       static_assert(KC / UMMA_K == 2, "two K = 16 steps per slab");
-      for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x, ++n_done) {
+      const uint32_t b_ring = b_resident ? (uint32_t)(steps_per_item * g.PW * g.kH) : (uint32_t)sl.n_b_stages;
+      const uint32_t b_stage16 = (uint32_t)(sl.b_stage_bytes >> 4);
+      const uint32_t b_lo_base = desc_lo(base + sl.off_b);
+      uint32_t bs = 0, b_par = 0, b_lo0 = b_lo_base;
+      const uint32_t n_a = (uint32_t)sl.n_a_bufs;
+      const uint32_t a_lo_buf0 = desc_lo(base + sl.off_a[0]), a_lo_buf1 = desc_lo(base + sl.off_a[1]);
+      uint32_t as = 0, a_par = 0;
+      const uint32_t kh_step16 = (uint32_t)(g.CBW * 4);    // one filter row further = CBW slab rows of 64 bytes
+      const int tail_chunk = (g.Cp - (g.n_chunks - 1) * KC > UMMA_K) ? -1 : g.n_chunks - 1;   // chunk with one K step only
+      const uint32_t a_half16 = (uint32_t)(2 * half) * slab16, b_half16 = (uint32_t)(2 * half) * B_SLAB16;
+      for (long long item = item0; item < g.n_items && alive; item += item_step, ++n_done) {
         const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
         const uint32_t use = (ACC_BUFS == 2) ? (n_done >> 1) : n_done;
         LAP(6);
-        if (!mbar_wait(acc_empty(ab), (use & 1u) ^ 1u, abort_word, ERR_MMA_ACC)) { alive = false; break; }
+        if (!MMA_WAIT(acc_empty(ab), (use & 1u) ^ 1u, abort_word, ERR_MMA_ACC)) { alive = false; break; }
         LAP(7);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem_base + (uint32_t)(ab * ACC_COLS);
-        bool first = true;
-        for (int step = 0; step < steps_per_item && alive; ++step) {
+        uint32_t acc0 = 0u;
+        for (int kd = 0; kd < g.kD && alive; ++kd)
+        for (int ch = 0; ch < g.n_chunks && alive; ++ch) {
           // a slab with at most 16 real channels (few-channel input, or the tail of C) needs one K = 16 step only
-          const bool k2 = g.Cp - ((step + rot) % g.n_chunks) * KC > UMMA_K;
+          const bool k2 = ch != tail_chunk;
           for (int w = 0; w < g.PW && alive; ++w) {
-            const int as = (int)(it_a % (uint32_t)sl.n_a_bufs);
-            if (!((g.dbg & 64u) ? mbar_poll(a_full(as), (it_a / (uint32_t)sl.n_a_bufs) & 1u, abort_word, ERR_MMA_A) : mbar_wait(a_full(as), (it_a / (uint32_t)sl.n_a_bufs) & 1u, abort_word, ERR_MMA_A))) { alive = false; break; }
+            LAP(9);
+            if (!MMA_WAIT(a_full((int)as), a_par, abort_word, ERR_MMA_A)) { alive = false; break; }
+            LAP(5);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             TL(9, it_a);
-            const uint32_t a_lo0 = desc_lo(base + sl.off_a[as]);
+            uint32_t a_lo_kh = (as ? a_lo_buf1 : a_lo_buf0) + a_half16;
             for (int kh = 0; kh < g.kH; ++kh) {
               LAP(0);
-              const int bs = b_resident ? (int)(it_b % (uint32_t)(steps_per_item * g.PW * g.kH)) : (int)(it_b % nbs);
               if (!(b_resident && n_done > 0))
-                if (!((g.dbg & 64u) ? mbar_poll(b_full(bs), b_resident ? 0u : ((it_b / nbs) & 1u), abort_word, ERR_MMA_B) : mbar_wait(b_full(bs), b_resident ? 0u : ((it_b / nbs) & 1u), abort_word, ERR_MMA_B))) { alive = false; break; }
+                if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) { alive = false; break; }   // TMA-written: CTA scope
               LAP(1); TL(0, it_b);
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-              const uint32_t b_lo0 = desc_lo(base + sl.off_b + bs * sl.b_stage_bytes);
-              const uint32_t a_lo_kh = a_lo0 + (uint32_t)(kh * g.CBW * 4);      // 64-byte rows = 4 descriptor units
-              const uint32_t acc0 = first ? 0u : 1u;
-              LAP(2);
               if (!(g.dbg & 8u)) {
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
                   uint32_t a_lo = a_lo_kh + (uint32_t)(mb * BM * 4);            // block mb starts RB * CBW = 128 rows later
-                  uint32_t b_lo = b_lo0;
+                  uint32_t b_lo = b_lo0 + b_half16;
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const uint32_t d_col = acc + (uint32_t)((mb * 4 + j) * BN);
-                    umma_f16_lohi(d_col, a_lo, b_lo, idesc, acc0);
-                    if (k2) umma_f16_lohi(d_col, a_lo + 2u, b_lo + 2u, idesc, 1u);   // second K = 16 step: 32 bytes further
+                  for (int jj = 0; jj < 2; ++jj) {
+                    const uint32_t d_col = acc + (uint32_t)((mb * 4 + 2 * half + jj) * BN);
+                    MMA_ISSUE(d_col, a_lo, b_lo, idesc, acc0);
+                    if (k2) MMA_ISSUE(d_col, a_lo + 2u, b_lo + 2u, idesc, 1u);   // second K = 16 step: 32 bytes further
                     a_lo += slab16;
-                    b_lo += (uint32_t)(BN * 64 / 16);
+                    b_lo += B_SLAB16;
                   }
                 }
               }
-              first = false;
+              acc0 = 1u;
               LAP(3); TL(1, it_b);
-              if (!b_resident) umma_commit(b_empty(bs));
+              if (!b_resident) MMA_COMMIT(b_empty((int)bs));
               LAP(4);
               ++it_b;
+              a_lo_kh += kh_step16;
+              b_lo0 += b_stage16;
+              if (++bs == b_ring) { bs = 0; b_lo0 = b_lo_base; b_par = b_resident ? 0u : (b_par ^ 1u); }
+              LAP(2);
             }
-            umma_commit(a_empty(as));
+            LAP(8);
+            MMA_COMMIT(a_empty((int)as));
+            LAP(6);
             ++it_a;
+            if (++as == n_a) { as = 0; a_par ^= 1u; }
           }
         }
-        umma_commit(acc_full(ab));
-        LAP(5);
+        MMA_COMMIT(acc_full(ab));
+        LAP(10);
       }
+#undef MMA_WAIT
+#undef MMA_ISSUE
+#undef MMA_COMMIT
 #ifdef WINO_ROW_TRACE
-      if (blockIdx.x == 0) for (int k = 0; k < 8; ++k) g_row_trace[16 + k] += lap_acc[k];
+      if (blockIdx.x == 0 && half == 0) for (int k = 0; k < 12; ++k) g_row_trace[16 + k] = lap_acc[k];
 #endif
     }
   } else {
@@ -508,16 +597,16 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     const bool vec_ok = (g.K % 8) == 0;
     uint32_t n_done = 0;
     bool alive = true;
-    for (long long item = blockIdx.x; item < g.n_items && alive; item += gridDim.x, ++n_done) {
+    for (long long item = item0; item < g.n_items && alive; item += item_step, ++n_done) {
       int n, od, rb, cb, nb;
       decode(item, n, od, rb, cb, nb);
       const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
       const uint32_t use = (ACC_BUFS == 2) ? (n_done >> 1) : n_done;
       unsigned got = 0;
-      if (lane == 0) got = mbar_wait(acc_full(ab), use & 1u, abort_word, ERR_EPI, (g.dbg & 32u) != 0) ? 1u : 0u;
+      if (lane == 0) got = mbar_wait(acc_full(ab), use & 1u, abort_word, ERR_EPI) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (got == 0u) { alive = false; break; }
-      if (warp == 11 && lane == 0) TL(6, n_done);
+      if (warp == 12 && lane == 0) TL(6, n_done);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int ow = (cb * g.CBW + tcp) * 2;
 #pragma unroll 1
@@ -534,8 +623,9 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (c0 + 16 >= BN && mb == MB - 1) {   // last columns are in registers: hand the accumulator back
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          mbar_arrive(acc_empty(ab));
-          if (warp == 11 && lane == 0) TL(7, n_done);
+          __syncwarp();
+          if (lane == 0) { if (PAIR) mbar_arrive_rank0(acc_empty(ab)); else mbar_arrive(acc_empty(ab)); }
+          if (warp == 12 && lane == 0) TL(7, n_done);
         }
         const int kbase = nb * BN + c0;
         float y0[16], y1[16];
@@ -555,7 +645,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             y0[c] = relu ? fmaxf(mx, 0.f) : mx;
           }
           const int ph = oh >> 1, pw = ow >> 1;
-          if ((tr & 1) == 0 && ph < g.yH && pw < g.yW && kbase < g.K && !(g.dbg & 16u)) {
+          if ((tr & 1) == 0 && ph < g.yH && pw < g.yW && kbase < g.K && n < g.N && !(g.dbg & 16u)) {
             T *dst = y + ((((long long)n * g.oD + od) * g.yH + ph) * g.yW + pw) * g.K + kbase;
             store16<T>(dst, y0, kbase, g.K, vec_ok);
           }
@@ -564,7 +654,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 #pragma unroll
             for (int c = 0; c < 16; ++c) { y0[c] = fmaxf(y0[c], 0.f); y1[c] = fmaxf(y1[c], 0.f); }
           }
-          if (oh < g.oH && kbase < g.K && !(g.dbg & 16u)) {
+          if (oh < g.oH && kbase < g.K && n < g.N && !(g.dbg & 16u)) {
             T *dst = y + ((((long long)n * g.oD + od) * g.oH + oh) * g.oW + ow) * g.K + kbase;
             if (ow < g.oW) store16<T>(dst, y0, kbase, g.K, vec_ok);
             if (ow + 1 < g.oW) store16<T>(dst + g.K, y1, kbase, g.K, vec_ok);
@@ -576,6 +666,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA frees tensor memory or exits while the other may still use it
 #ifdef WINO_ROW_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     g_row_trace[0] += (unsigned long long)(clock64() - trace_kernel_t0);
@@ -584,7 +675,8 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 #endif
   if (warp == 10) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
@@ -664,26 +756,18 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   const int Cp = (d.C + 7) / 8 * 8;
   p.Cp = Cp;
   p.PW = (d.kW + 2) / 3;
-  // Work item: MB tile blocks stacked along H x BN output channels, MB * BN = 128 (the 512 TMEM columns hold
-  // MB x 4 positions x BN).  Two blocks x 64 channels halve the filter bytes streamed per multiply-add, which is
-  // what the kernel runs out of first; one block x 128 channels is kept for images too short for two blocks.
-  // WINOCONV_ROW_MB=1|2 forces the choice (tuning).
+  // Work item: MB tile blocks stacked along H x BN output channels, MB * BN <= 128 (the 512 TMEM columns hold
+  // MB x 4 positions x BN).  One block x 128 channels is the default.  Two blocks x 64 channels halve the filter
+  // bytes streamed per multiply-add but were measured slower on B200 (VGG-16: 17.3 vs 11.9 ms): an N = 64 MMA
+  // takes as long as an N = 128 one, and two blocks leave room for only one slab buffer.  WINOCONV_ROW_MB=2
+  // selects them for experiments.
   const int ncp = (d.oW + 1) / 2;
   auto padded = [&](int rows_item, int cbw) {
     return (long long)((d.oH + rows_item - 1) / rows_item) * rows_item * ((ncp + cbw - 1) / cbw) * cbw;
   };
-  int best_mb = 0, best_cbw = 0;
-  long long best = -1;
   static const int forced_mb = [] { const char *v = getenv("WINOCONV_ROW_MB"); return v && *v ? atoi(v) : 0; }();
-  for (int mb = 2; mb >= 1; --mb) {
-    if (forced_mb && mb != forced_mb) continue;
-    for (int cbw : {16, 8}) {
-      const long long vol = padded(mb * (128 / cbw), cbw);
-      // prefer two blocks unless that pads more than 15 % over the best one-block shape
-      const long long score = mb == 2 ? vol * 100 : vol * 115;
-      if (best < 0 || score < best) { best = score; best_mb = mb; best_cbw = cbw; }
-    }
-  }
+  const int best_mb = forced_mb == 2 ? 2 : 1;
+  const int best_cbw = padded(best_mb * 8, 16) <= padded(best_mb * 16, 8) ? 16 : 8;
   p.MB = best_mb;
   p.BN = (p.MB == 2 || d.K <= 64) ? 64 : 128;
   p.CBW = best_cbw;
@@ -697,13 +781,19 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   p.n_nblocks = (d.K + p.BN - 1) / p.BN;
   p.slabs = d.kD * d.kH * p.PW * 4;
   p.filter_elems = (long long)p.slabs * d.K * Cp;
-  p.n_items = (long long)d.N * d.oD * p.n_rb * p.n_cb * p.n_nblocks;
+  // CTA pairs: the two SMs of a cluster take images 2n and 2n + 1 of one item and share every filter slab (each loads
+  // half of it), which halves the filter bytes an SM pulls per multiply-add.  Used when the slabs are streamed (more
+  // than one channel block, or an item's slabs do not fit the stage ring) and the accumulator is 128 channels wide.
+  static const int pair_env = [] { const char *v = getenv("WINOCONV_ROW_PAIR"); return v && *v ? atoi(v) : -1; }();
+  p.pair = (pair_env != 0 && p.BN == 128 && p.MB == 1 && d.N >= 2 &&
+            (p.n_nblocks > 1 || p.n_chunks * d.kD * d.kH * p.PW > 6)) ? 1 : 0;
+  p.n_items = (long long)(p.pair ? (d.N + 1) / 2 : d.N) * d.oD * p.n_rb * p.n_cb * p.n_nblocks;
   if (p.patch_w > 256 || p.patch_h > 256) return false;
   // shared memory: 2 raw patches, 2 slab sets (1 if two do not leave room for 3 filter stages), then as many
   // filter stages as fit (2..8)
   const int raw_bytes = ((p.patch_h * p.patch_w * KC * 2 + 127) / 128) * 128;
   const int a_bytes = ((4 * p.slab_rows * 64 + 1023) / 1024) * 1024;
-  const int b_stage = 4 * p.BN * 64;
+  const int b_stage = 4 * (p.pair ? p.BN / 2 : p.BN) * 64;
   const int budget = 227 * 1024;
   int n_a = 2;
   int fixed = 2 * raw_bytes + n_a * a_bytes + 1024 /*bars*/ + 1024 /*align*/;
@@ -731,11 +821,11 @@ cudaError_t launch_rowfused_filter_transform(const RowDesc &d, const RowPlan &p,
   return cudaGetLastError();
 }
 
-template <typename T, int BN, int MB>
+template <typename T, int BN, int MB, bool PAIR>
 static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorMap &mx, const CUtensorMap &mu, void *y,
                              const void *bias, int sm_count, uint32_t idesc, cudaStream_t s, const char **detail) {
   using namespace rowf;
-  auto kern = rowfused_kernel<T, BN, MB>;
+  auto kern = rowfused_kernel<T, BN, MB, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_total);
   if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
   RGeom g;
@@ -756,6 +846,25 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   sl.off_raw[1] = sl.off_raw[0] + p.raw_bytes;
   sl.off_bars = sl.off_raw[1] + p.raw_bytes;
   sl.total = p.smem_total;
+  if (PAIR) {
+    const int pairs = (int)std::min<long long>(p.n_items, sm_count / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(N_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)p.smem_total;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // one resident pair per two SMs where the GPCs allow it; fewer pairs when they do not (the items are strided over
+    // the pairs launched, so every launched pair must be resident)
+    int max_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0 && max_clusters < pairs)
+      cfg.gridDim = dim3((unsigned)(2 * max_clusters), 1, 1);
+    return cudaLaunchKernelEx(&cfg, kern, mx, mu, (T *)y, (const T *)bias, g, sl, idesc);
+  }
   const int grid = (int)std::min<long long>(p.n_items, sm_count);
   kern<<<grid, N_THREADS, p.smem_total, s>>>(mx, mu, (T *)y, (const T *)bias, g, sl, idesc);
   return cudaGetLastError();
@@ -797,7 +906,7 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   {
     const cuuint64_t dims[3] = {(cuuint64_t)p.Cp, (cuuint64_t)d.K, (cuuint64_t)p.slabs};
     const cuuint64_t st[2] = {(cuuint64_t)p.Cp * 2ull, (cuuint64_t)p.Cp * 2ull * d.K};
-    const cuuint32_t box[3] = {(cuuint32_t)KC, (cuuint32_t)p.BN, 1u};
+    const cuuint32_t box[3] = {(cuuint32_t)KC, (cuuint32_t)(p.pair ? p.BN / 2 : p.BN), 1u};
     const cuuint32_t es[3] = {1u, 1u, 1u};
     if (enc(&mu, dt, 3, const_cast<void *>(u), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
@@ -810,15 +919,18 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) { *detail = "cudaDeviceGetAttribute(MultiProcessorCount) failed"; return e; }
   const uint32_t fmt = dtype == WINOCONV_F16 ? 0u : 1u;
-  const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-  if (dtype == WINOCONV_F16) {
-    if (p.MB == 2) return launch_rf<__half, 64, 2>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
-    return p.BN == 64 ? launch_rf<__half, 64, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)
-                      : launch_rf<__half, 128, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
-  }
-  if (p.MB == 2) return launch_rf<__nv_bfloat16, 64, 2>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
-  return p.BN == 64 ? launch_rf<__nv_bfloat16, 64, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)
-                    : launch_rf<__nv_bfloat16, 128, 1>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);
+  const uint32_t m_rows = p.pair ? 2u * BM : (uint32_t)BM;   // a pair's MMA spans the tile blocks of both CTAs
+  const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((m_rows >> 4) << 24);
+#define ROWF_DISPATCH(T)                                                                                         \
+  do {                                                                                                           \
+    if (p.pair) return launch_rf<T, 128, 1, true>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);            \
+    if (p.MB == 2) return launch_rf<T, 64, 2, false>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);         \
+    return p.BN == 64 ? launch_rf<T, 64, 1, false>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)            \
+                      : launch_rf<T, 128, 1, false>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);          \
+  } while (0)
+  if (dtype == WINOCONV_F16) ROWF_DISPATCH(__half);
+  ROWF_DISPATCH(__nv_bfloat16);
+#undef ROWF_DISPATCH
 }
 
 #ifdef WINO_ROW_TRACE
