@@ -16,8 +16,8 @@
 //   warp 0       TMA: raw input patch (5-D box, zero fill = padding) per 32-channel slab
 //   warps 1-8    F(2,3) along W on the patch: raw -> four [rows x 32] slabs, 64-byte swizzle, fence.proxy.async
 //   warp 9       TMA: transformed-filter slabs of the current (kd, kh, window), four positions per stage
-//   warps 10-11  tcgen05.mma (M = 128, N = BN, K = 16) issue + commits, two positions each; warp 10: TMEM alloc
-//   warps 12-15  epilogue: tcgen05.ld, A^T along W, bias / ReLU / 2x2 max-pool (row partner by shuffle), 32-byte stores
+//   warps 10-13  tcgen05.mma (M = 128, N = BN, K = 16) issue + commits, one position each; warp 10: TMEM alloc
+//   warps 14-21  epilogue (lane quarter x column half): tcgen05.ld, A^T along W, bias / ReLU / 2x2 max-pool (row partner by shuffle), 32-byte stores
 // V and M never exist in global memory.  Every mbarrier wait is bounded and reports through the error word.
 // With a batch of two or more and streamed filter slabs the CTAs run as pairs (clusters of two, cta_group::2):
 // one M = 256 MMA covers the tile blocks of both, and each loads only its half of every filter slab.
@@ -56,8 +56,9 @@ constexpr int BM = 128;            // tiles per block == TMEM lanes
 constexpr int KC = 32;             // reduction slab (channels): 64-byte rows
 constexpr int UMMA_K = 16;
 constexpr int N_PROD = 256;
-constexpr int N_THREADS = 512;     // 16 warps
-constexpr int N_MMA_THREADS = 2;   // MMA issuers: thread h takes positions 2h and 2h + 1 of every stage
+constexpr int N_THREADS = 704;     // 22 warps
+constexpr int EPI_WARP0 = 14;      // first of the eight epilogue warps
+constexpr int N_MMA_THREADS = 4;   // MMA issuers: one per Winograd position (its own accumulator columns)
 constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;
 
 enum ErrCode : unsigned {
@@ -150,6 +151,14 @@ __device__ __forceinline__ void umma_f16_lohi(uint32_t tmem_d, uint32_t a_lo, ui
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Warp-uniform wait: every lane polls, the outcome is voted.  The single-thread roles (TMA issue, MMA issue) run their
+// loops with the whole warp converged and predicate only the issuing instructions on lane 0: a lone lane looping
+// while its 31 siblings sit at the final barrier pays ~200 clocks at every taken branch.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
+  const bool ok = mbar_wait(bar, parity, abort_word, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---- CTA pairs (cluster of two, tcgen05 cta_group::2): one MMA spans both SMs (M = 256: 128 tiles from each), each
 // SM loads only its half of every filter slab, so the filter bytes an SM pulls from L2 per multiply-add halve.
 // The even CTA of the pair (rank 0) issues the MMAs; barriers it waits on collect arrivals from both CTAs.
@@ -218,6 +227,12 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+
 template <typename T> struct P2;
 template <> struct P2<__half> {
   using V = __half2;
@@ -241,19 +256,25 @@ template <typename T> __device__ __forceinline__ V8<T> v8_sub(const V8<T> &a, co
   return r;
 }
 
-// 16 consecutive output channels of one pixel: two 16-byte stores (K a multiple of 8) or element-wise.
+// 16 consecutive output channels of one pixel, already packed to 16-bit pairs.  mode 2: one 32-byte store (K a
+// multiple of 16, 32-byte aligned output) -- a warp's store touches one line per lane whatever its width, so wider
+// stores halve the time the epilogue spends in the load/store unit; mode 1: 16-byte stores; mode 0: element-wise.
 template <typename T>
-__device__ __forceinline__ void store16(T *dst, const float (&v)[16], int kbase, int K, bool vec_ok) {
-  if (vec_ok) {
-    typename P2<T>::V pk[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) pk[c] = P2<T>::from(v[2 * c], v[2 * c + 1]);
-    *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(&pk[0]);
-    if (kbase + 8 < K) *reinterpret_cast<uint4 *>(dst + 8) = *reinterpret_cast<const uint4 *>(&pk[4]);
+__device__ __forceinline__ void store16p(T *dst, const uint32_t (&pk)[8], int kbase, int K, int mode) {
+  if (mode == 2) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
+                 "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]) : "memory");
+  } else if (mode == 1) {
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    if (kbase + 8 < K) *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
   } else {
 #pragma unroll
-    for (int c = 0; c < 16; ++c)
-      if (kbase + c < K) Elem<T>::store(dst + c, v[c]);
+    for (int c = 0; c < 16; ++c) {
+      if (kbase + c < K) {
+        const unsigned short bits = (unsigned short)((pk[c >> 1] >> ((c & 1) * 16)) & 0xFFFFu);
+        *reinterpret_cast<unsigned short *>(dst + c) = bits;
+      }
+    }
   }
 }
 
@@ -319,7 +340,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       mbar_init(a_full(i), PAIR ? 2 * (N_PROD / 32) : N_PROD / 32);
       mbar_init(a_empty(i), N_MMA_THREADS);                      // one commit per MMA-issuing thread
       mbar_init(acc_full(i), N_MMA_THREADS);
-      mbar_init(acc_empty(i), PAIR ? 8 : 4);                     // one arrival per epilogue warp
+      mbar_init(acc_empty(i), PAIR ? 16 : 8);                    // one arrival per epilogue warp
     }
     for (int i = 0; i < 8; ++i) {
       mbar_init(b_full(i), 1);
@@ -366,7 +387,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 
   if (warp == 0) {
     // ---------------------------------------------------------------- raw input patches
-    if (lane == 0) {
+    {
       uint32_t it = 0;
       bool alive = true;
       for (long long item = item0; item < g.n_items && alive; item += item_step) {
@@ -375,11 +396,13 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks; ++ch) {
             const int s = it & 1;
-            if (!mbar_wait(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
-            if (g.dbg & 2u) { mbar_arrive(raw_full(s)); ++it; continue; }
-            mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
-            tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
-                        od + kd - g.pD, n);
+            if (!mbar_wait_warp(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
+            if (g.dbg & 2u) { if (lane == 0) mbar_arrive(raw_full(s)); ++it; continue; }
+            if (lane == 0) {
+              mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
+              tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
+                          od + kd - g.pD, n);
+            }
             ++it;
           }
       }
@@ -442,7 +465,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- transformed-filter slabs
-    if (lane == 0) {
+    {
       uint32_t it = 0;
       bool alive = true;
       const int nbs = sl.n_b_stages;
@@ -457,10 +480,12 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           for (int ch = 0; ch < g.n_chunks && alive; ++ch)
             for (int w = 0; w < g.PW && alive; ++w)
               for (int kh = 0; kh < g.kH; ++kh) {
-                if (!mbar_wait(b_empty(s), s_par, abort_word, ERR_B_EMPTY)) { alive = false; break; }
-                TL(2, it);
+                if (!mbar_wait_warp(b_empty(s), s_par, abort_word, ERR_B_EMPTY)) { alive = false; break; }
+                if (lane == 0) TL(2, it);
                 const int slab0 = ((kd * g.kH + kh) * g.PW + w) * 4;
-                if (PAIR) {   // this CTA's half (BN / 2 rows) of each slab; rank 0 expects the bytes of both halves
+                if (lane != 0) {
+                  // only lane 0 issues
+                } else if (PAIR) {   // this CTA's half (BN / 2 rows) of each slab; rank 0 expects the bytes of both halves
                   if (rank == 0) mbar_expect_tx(b_full(s), 2u * (uint32_t)sl.b_stage_bytes);
 #pragma unroll
                   for (int j = 0; j < 4; ++j)
@@ -472,7 +497,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
                   for (int j = 0; j < 4; ++j)
                     tma_load_3d(dst + j * (BN * 64), &map_u, b_full(s), ch * KC, nb * BN, slab0 + j);
                 }
-                TL(3, it);
+                if (lane == 0) TL(3, it);
                 ++it;
                 dst += (uint32_t)sl.b_stage_bytes;
                 if (++s == nbs) { s = 0; s_par ^= 1u; dst = base + sl.off_b; }
@@ -483,23 +508,23 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         while (clock64() - start < 2000000LL) { }
       }
     }
-  } else if (warp == 10 || warp == 11) {
+  } else if (warp >= 10 && warp < 10 + N_MMA_THREADS) {
     // ---------------------------------------------------------------- MMA issue (rank 0 of a pair issues for both CTAs)
     // Issuing one tcgen05.mma costs the thread about as long as an N = 128 MMA runs (~60 clocks), so whatever else
-    // a single issuer does (barrier waits, commits, loop branches) is time the tensor pipe idles.  Two threads in
-    // two warps each issue half of every stage (their own two of the four positions, i.e. their own accumulator
-    // columns); while one waits or commits the other keeps the pipe fed.
-    const int half = warp - 10;
-    if (lane == 0 && rank == 0) {
-#define MMA_WAIT(bar_, par_, aw_, code_) mbar_wait(bar_, par_, aw_, code_)
-#define MMA_ISSUE(d_, a_, b_, i_, acc_) do { if (PAIR) umma_f16_lohi_pair(d_, a_, b_, i_, acc_); else umma_f16_lohi(d_, a_, b_, i_, acc_); } while (0)
-#define MMA_COMMIT(bar_) do { if (PAIR) umma_commit_pair(bar_); else umma_commit(bar_); } while (0)
+    // a single issuer does (barrier waits, commits, loop branches) is time the tensor pipe idles.  Four warps, one
+    // per scheduler, each issue one of the four positions of every stage (their own accumulator columns); while
+    // one waits or commits the others keep the pipe fed.
+    const int half = warp - 10;                        // position this warp issues
+    if (rank == 0) {
+#define MMA_WAIT(bar_, par_, aw_, code_) mbar_wait(bar_, par_, aw_, code_)   /* every lane polls; lanes differ only when a wait gives up */
+#define MMA_ISSUE(d_, a_, b_, i_, acc_) do { if (PAIR) umma_f16_lohi_pair(d_, a_, b_, i_, acc_); else umma_f16_lohi(d_, a_, b_, i_, acc_); } while (0)   /* inside if (lane == 0) */
+#define MMA_COMMIT(bar_) do { if (lane == 0) { if (PAIR) umma_commit_pair(bar_); else umma_commit(bar_); } } while (0)
       uint32_t it_a = 0, it_b = 0, n_done = 0;
       bool alive = true;
 #ifdef WINO_ROW_TRACE
       // LAP(k): clocks since the previous LAP are charged to segment k (register accumulators, written once)
       unsigned lap_t = (unsigned)clock();
-      unsigned lap_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+      unsigned lap_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #define LAP(k) do { if (half == 0) { const unsigned now_ = (unsigned)clock(); lap_acc[k] += now_ - lap_t; lap_t = now_; } } while (0)
 #else
 #define LAP(k) do { } while (0)
@@ -518,8 +543,11 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       uint32_t as = 0, a_par = 0;
       const uint32_t kh_step16 = (uint32_t)(g.CBW * 4);    // one filter row further = CBW slab rows of 64 bytes
       const int tail_chunk = (g.Cp - (g.n_chunks - 1) * KC > UMMA_K) ? -1 : g.n_chunks - 1;   // chunk with one K step only
-      const uint32_t a_half16 = (uint32_t)(2 * half) * slab16, b_half16 = (uint32_t)(2 * half) * B_SLAB16;
-      for (long long item = item0; item < g.n_items && alive; item += item_step, ++n_done) {
+      const int kH = g.kH, PW = g.PW, n_chunks = g.n_chunks;   // loop bounds in registers
+      const long long n_items = g.n_items;
+      const bool skip_mma = (g.dbg & 8u) != 0;
+      const uint32_t a_half16 = (uint32_t)half * slab16, b_half16 = (uint32_t)half * B_SLAB16;
+      for (long long item = item0; item < n_items && alive; item += item_step, ++n_done) {
         const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
         const uint32_t use = (ACC_BUFS == 2) ? (n_done >> 1) : n_done;
         LAP(6);
@@ -528,39 +556,37 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem_base + (uint32_t)(ab * ACC_COLS);
         uint32_t acc0 = 0u;
-        for (int kd = 0; kd < g.kD && alive; ++kd)
-        for (int ch = 0; ch < g.n_chunks && alive; ++ch) {
+        int ch = 0;
+        for (int step = 0; step < steps_per_item && alive; ++step) {
           // a slab with at most 16 real channels (few-channel input, or the tail of C) needs one K = 16 step only
+          LAP(14);
           const bool k2 = ch != tail_chunk;
-          for (int w = 0; w < g.PW && alive; ++w) {
+          if (++ch == n_chunks) ch = 0;
+          LAP(15);
+          for (int w = 0; w < PW && alive; ++w) {
             LAP(9);
             if (!MMA_WAIT(a_full((int)as), a_par, abort_word, ERR_MMA_A)) { alive = false; break; }
             LAP(5);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            TL(9, it_a);
+            if (lane == 0) TL(9, it_a);
             uint32_t a_lo_kh = (as ? a_lo_buf1 : a_lo_buf0) + a_half16;
-            for (int kh = 0; kh < g.kH; ++kh) {
+            for (int kh = 0; kh < kH; ++kh) {
               LAP(0);
               if (!(b_resident && n_done > 0))
-                if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) { alive = false; break; }   // TMA-written: CTA scope
-              LAP(1); TL(0, it_b);
-              if (!(g.dbg & 8u)) {
+                if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) { alive = false; break; }
+              LAP(1); if (lane == 0) TL(0, it_b);
+              if (!skip_mma && lane == 0) {
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
-                  uint32_t a_lo = a_lo_kh + (uint32_t)(mb * BM * 4);            // block mb starts RB * CBW = 128 rows later
-                  uint32_t b_lo = b_lo0 + b_half16;
-#pragma unroll
-                  for (int jj = 0; jj < 2; ++jj) {
-                    const uint32_t d_col = acc + (uint32_t)((mb * 4 + 2 * half + jj) * BN);
-                    MMA_ISSUE(d_col, a_lo, b_lo, idesc, acc0);
-                    if (k2) MMA_ISSUE(d_col, a_lo + 2u, b_lo + 2u, idesc, 1u);   // second K = 16 step: 32 bytes further
-                    a_lo += slab16;
-                    b_lo += B_SLAB16;
-                  }
+                  const uint32_t a_lo = a_lo_kh + (uint32_t)(mb * BM * 4);      // block mb starts RB * CBW = 128 rows later
+                  const uint32_t b_lo = b_lo0 + b_half16;
+                  const uint32_t d_col = acc + (uint32_t)((mb * 4 + half) * BN);
+                  MMA_ISSUE(d_col, a_lo, b_lo, idesc, acc0);
+                  if (k2) MMA_ISSUE(d_col, a_lo + 2u, b_lo + 2u, idesc, 1u);     // second K = 16 step: 32 bytes further
                 }
               }
               acc0 = 1u;
-              LAP(3); TL(1, it_b);
+              LAP(3); if (lane == 0) TL(1, it_b);
               if (!b_resident) MMA_COMMIT(b_empty((int)bs));
               LAP(4);
               ++it_b;
@@ -574,7 +600,10 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             LAP(6);
             ++it_a;
             if (++as == n_a) { as = 0; a_par ^= 1u; }
+            LAP(11);
+            LAP(12);
           }
+          LAP(13);
         }
         MMA_COMMIT(acc_full(ab));
         LAP(10);
@@ -583,18 +612,25 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 #undef MMA_ISSUE
 #undef MMA_COMMIT
 #ifdef WINO_ROW_TRACE
-      if (blockIdx.x == 0 && half == 0) for (int k = 0; k < 12; ++k) g_row_trace[16 + k] = lap_acc[k];
+      if (blockIdx.x == 0 && half == 0 && lane == 0) for (int k = 0; k < 16; ++k) g_row_trace[16 + k] = lap_acc[k];
 #endif
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    // Eight warps: warp w reads TMEM lane quarter w & 3 (a hardware rule) and one half of the accumulator columns.
     const int qd = warp & 3;                           // TMEM lane quarter
+    const int chalf = (warp - EPI_WARP0) >> 2;         // which half of the BN columns
     const int row = qd * 32 + lane;                    // tile of the block: (out row, column pair)
-    const int tr = row / g.CBW, tcp = row - tr * g.CBW;
+    const int cbw_shift = g.CBW == 16 ? 4 : 3;
+    const int tr = row >> cbw_shift, tcp = row - (tr << cbw_shift);
     const bool relu = (g.epilogue & WINOCONV_EPI_RELU) != 0;
     const bool has_bias = (g.epilogue & WINOCONV_EPI_BIAS) != 0;
     const bool pool = (g.epilogue & WINOCONV_EPI_POOL2) != 0;
-    const bool vec_ok = (g.K % 8) == 0;
+    // widest store the output allows: 32 bytes (K % 16, 32-byte aligned base), 16 bytes (K % 8), or elements
+    const int st_mode = ((g.K % 16) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0) ? 2 : ((g.K % 8) == 0 ? 1 : 0);
+    const bool no_store = (g.dbg & 16u) != 0;
+    const int K = g.K;
+    constexpr int C_PER_WARP = BN / 2;
     uint32_t n_done = 0;
     bool alive = true;
     for (long long item = item0; item < g.n_items && alive; item += item_step, ++n_done) {
@@ -606,61 +642,86 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       if (lane == 0) got = mbar_wait(acc_full(ab), use & 1u, abort_word, ERR_EPI) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (got == 0u) { alive = false; break; }
-      if (warp == 12 && lane == 0) TL(6, n_done);
+      if (warp == EPI_WARP0 && lane == 0) TL(6, n_done);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int ow = (cb * g.CBW + tcp) * 2;
+      const int k0 = nb * BN + chalf * C_PER_WARP;      // first output channel of this warp
 #pragma unroll 1
       for (int mb = 0; mb < MB; ++mb) {
-      const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(ab * ACC_COLS + mb * 4 * BN);
-      const int oh = (rb * MB + mb) * g.RB + tr;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        uint32_t m0[16], m1[16], m2[16], m3[16];
-        tmem_ld_x16(t_lane + (uint32_t)(0 * BN + c0), m0);
-        tmem_ld_x16(t_lane + (uint32_t)(1 * BN + c0), m1);
-        tmem_ld_x16(t_lane + (uint32_t)(2 * BN + c0), m2);
-        tmem_ld_x16(t_lane + (uint32_t)(3 * BN + c0), m3);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 16 >= BN && mb == MB - 1) {   // last columns are in registers: hand the accumulator back
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) { if (PAIR) mbar_arrive_rank0(acc_empty(ab)); else mbar_arrive(acc_empty(ab)); }
-          if (warp == 12 && lane == 0) TL(7, n_done);
-        }
-        const int kbase = nb * BN + c0;
-        float y0[16], y1[16];
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float a0 = __uint_as_float(m0[c]), a1 = __uint_as_float(m1[c]), a2 = __uint_as_float(m2[c]), a3 = __uint_as_float(m3[c]);
-          float bv = 0.f;
-          if (has_bias && kbase + c < g.K) bv = Elem<T>::load(bias + kbase + c);
-          y0[c] = a0 + a1 + a2 + bv;
-          y1[c] = a1 - a2 - a3 + bv;
-        }
+        const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(ab * ACC_COLS + mb * 4 * BN + chalf * C_PER_WARP);
+        const int oh = (rb * MB + mb) * g.RB + tr;
+        // destination of this thread's tile, and which of its stores are inside the output
+        T *dst;
+        bool st0, st1;
         if (pool) {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            float mx = fmaxf(y0[c], y1[c]);
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, g.CBW));   // the other output row of the 2x2 window
-            y0[c] = relu ? fmaxf(mx, 0.f) : mx;
-          }
           const int ph = oh >> 1, pw = ow >> 1;
-          if ((tr & 1) == 0 && ph < g.yH && pw < g.yW && kbase < g.K && n < g.N && !(g.dbg & 16u)) {
-            T *dst = y + ((((long long)n * g.oD + od) * g.yH + ph) * g.yW + pw) * g.K + kbase;
-            store16<T>(dst, y0, kbase, g.K, vec_ok);
-          }
+          dst = y + ((((long long)n * g.oD + od) * g.yH + ph) * g.yW + pw) * K + k0;
+          st0 = (tr & 1) == 0 && ph < g.yH && pw < g.yW && n < g.N && !no_store;
+          st1 = false;
         } else {
-          if (relu) {
+          dst = y + ((((long long)n * g.oD + od) * g.oH + oh) * g.oW + ow) * K + k0;
+          const bool in = oh < g.oH && n < g.N && !no_store;
+          st0 = in && ow < g.oW;
+          st1 = in && ow + 1 < g.oW;
+        }
+        uint32_t p0[8], p1[8], p2[8], p3[8];
+#pragma unroll 1
+        for (int c0 = 0; c0 < C_PER_WARP; c0 += 16) {
+          uint32_t pk0[8], pk1[8];                     // 16 channels of the two output pixels, packed
 #pragma unroll
-            for (int c = 0; c < 16; ++c) { y0[c] = fmaxf(y0[c], 0.f); y1[c] = fmaxf(y1[c], 0.f); }
+          for (int h = 0; h < 2; ++h) {
+            const int cc = c0 + 8 * h;
+            tmem_ld_x8(t_lane + (uint32_t)(0 * BN + cc), p0);
+            tmem_ld_x8(t_lane + (uint32_t)(1 * BN + cc), p1);
+            tmem_ld_x8(t_lane + (uint32_t)(2 * BN + cc), p2);
+            tmem_ld_x8(t_lane + (uint32_t)(3 * BN + cc), p3);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (h == 1 && c0 + 16 >= C_PER_WARP && mb == MB - 1) {   // last columns are in registers: hand the accumulator back
+              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) { if (PAIR) mbar_arrive_rank0(acc_empty(ab)); else mbar_arrive(acc_empty(ab)); }
+              if (warp == EPI_WARP0 && lane == 0) TL(7, n_done);
+            }
+            const int kbase = k0 + cc;
+            float y0[8], y1[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const float a0 = __uint_as_float(p0[c]), a1 = __uint_as_float(p1[c]), a2 = __uint_as_float(p2[c]), a3 = __uint_as_float(p3[c]);
+              y0[c] = a0 + a1 + a2;
+              y1[c] = a1 - a2 - a3;
+            }
+            if (has_bias) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const float bv = (kbase + c < K) ? Elem<T>::load(bias + kbase + c) : 0.f;
+                y0[c] += bv;
+                y1[c] += bv;
+              }
+            }
+            if (pool) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                float mx = fmaxf(y0[c], y1[c]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, g.CBW));   // the other output row of the 2x2 window
+                y0[c] = relu ? fmaxf(mx, 0.f) : mx;
+              }
+            } else if (relu) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) { y0[c] = fmaxf(y0[c], 0.f); y1[c] = fmaxf(y1[c], 0.f); }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const typename P2<T>::V v0 = P2<T>::from(y0[2 * c], y0[2 * c + 1]), v1 = P2<T>::from(y1[2 * c], y1[2 * c + 1]);
+              pk0[4 * h + c] = *reinterpret_cast<const uint32_t *>(&v0);
+              pk1[4 * h + c] = *reinterpret_cast<const uint32_t *>(&v1);
+            }
           }
-          if (oh < g.oH && kbase < g.K && n < g.N && !(g.dbg & 16u)) {
-            T *dst = y + ((((long long)n * g.oD + od) * g.oH + oh) * g.oW + ow) * g.K + kbase;
-            if (ow < g.oW) store16<T>(dst, y0, kbase, g.K, vec_ok);
-            if (ow + 1 < g.oW) store16<T>(dst + g.K, y1, kbase, g.K, vec_ok);
+          const int kb16 = k0 + c0;
+          if (kb16 < K) {
+            if (st0) store16p<T>(dst + c0, pk0, kb16, K, st_mode);
+            if (st1) store16p<T>(dst + K + c0, pk1, kb16, K, st_mode);
           }
         }
-      }
       }
     }
   }
