@@ -295,6 +295,7 @@ def run_ours(args):
         metric = "conv_images_per_s"
     x_dev = x_host.to(dev, non_blocking=True)
     y_host = torch.empty(model.out_shape, dtype=torch.float16).pin_memory()
+    y_probe = torch.empty(model.out_shape, dtype=torch.float16, device=dev)
     torch.cuda.synchronize(dev)
 
     use_graph = not args.no_graph
@@ -324,13 +325,18 @@ def run_ours(args):
 
     # ---- region 2: end to end from pinned host memory ---------------------------------------------
     # Every step copies its batch host -> device and its result device -> host.  The copies run on their own
-    # stream into two alternating input buffers, so the H2D copy of step i+1 overlaps the kernels of step i;
-    # all copies of the K timed steps lie between the two events.
+    # streams: H2D into two alternating input buffers, so the copy of step i+1 overlaps the kernels of step i; the
+    # result is moved to one of two staging buffers (device to device) and read back from there while the next
+    # step computes.  All copies of the K timed steps lie between the two events.
     main = torch.cuda.current_stream(dev)
     copy_stream = torch.cuda.Stream(device=dev)
+    d2h_stream = torch.cuda.Stream(device=dev)
     x_bufs = [x_dev, torch.empty_like(x_dev)]
     copied = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
+    y_stage = [torch.empty_like(y_probe), torch.empty_like(y_probe)]
+    staged = [torch.cuda.Event() for _ in range(2)]
+    read_back = [torch.cuda.Event() for _ in range(2)]
 
     def issue_copy(i):
         b = i % 2
@@ -342,7 +348,9 @@ def run_ours(args):
     def run_e2e(n_steps):
         for b in range(2):
             consumed[b].record(main)
+            read_back[b].record(main)
         copy_stream.wait_stream(main)
+        d2h_stream.wait_stream(main)
         issue_copy(0)
         for i in range(n_steps):
             b = i % 2
@@ -351,8 +359,15 @@ def run_ours(args):
             main.wait_event(copied[b])
             y = model.forward(x_bufs[b])
             consumed[b].record(main)
-            y_host.copy_(y, non_blocking=True)
+            main.wait_event(read_back[b])          # the staging buffer's previous read-back has finished
+            y_stage[b].copy_(y, non_blocking=True)
+            staged[b].record(main)
+            d2h_stream.wait_event(staged[b])
+            with torch.cuda.stream(d2h_stream):
+                y_host.copy_(y_stage[b], non_blocking=True)
+                read_back[b].record(d2h_stream)
         main.wait_stream(copy_stream)
+        main.wait_stream(d2h_stream)
 
     run_e2e(3)
     barrier()

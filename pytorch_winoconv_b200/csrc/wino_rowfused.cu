@@ -14,10 +14,10 @@
 //
 // One persistent CTA per SM; per work item (tile block x 64/128 output channels):
 //   warp 0       TMA: raw input patch (5-D box, zero fill = padding) per 32-channel slab
-//   warps 1-8    F(2,3) along W on the patch: raw -> four [rows x 32] slabs, 64-byte swizzle, fence.proxy.async
-//   warp 9       TMA: transformed-filter slabs of the current (kd, kh, window), four positions per stage
-//   warps 10-13  tcgen05.mma (M = 128, N = BN, K = 16) issue + commits, one position each; warp 10: TMEM alloc
-//   warps 14-21  epilogue (lane quarter x column half): tcgen05.ld, A^T along W, bias / ReLU / 2x2 max-pool (row partner by shuffle), 32-byte stores
+//   warps 1-10   F(2,3) along W on the patch: raw -> four [rows x 32] slabs, 64-byte swizzle, fence.proxy.async
+//   warp 11      TMA: transformed-filter slabs of the current (kd, kh, window), four positions per stage
+//   warps 12-15  tcgen05.mma (M = 128, N = BN, K = 16) issue + commits, one position each; warp 12: TMEM alloc
+//   warps 16-23  epilogue (lane quarter x column half): tcgen05.ld, A^T along W, bias / ReLU / 2x2 max-pool (row partner by shuffle), 32-byte stores
 // V and M never exist in global memory.  Every mbarrier wait is bounded and reports through the error word.
 // With a batch of two or more and streamed filter slabs the CTAs run as pairs (clusters of two, cta_group::2):
 // one M = 256 MMA covers the tile blocks of both, and each loads only its half of every filter slab.
@@ -55,9 +55,11 @@ namespace rowf {
 constexpr int BM = 128;            // tiles per block == TMEM lanes
 constexpr int KC = 32;             // reduction slab (channels): 64-byte rows
 constexpr int UMMA_K = 16;
-constexpr int N_PROD = 256;
-constexpr int N_THREADS = 704;     // 22 warps
-constexpr int EPI_WARP0 = 14;      // first of the eight epilogue warps
+constexpr int N_PROD = 320;        // 10 producer warps: a slab set of 160 rows x 4 vectors is two full rounds
+constexpr int B_WARP = 1 + N_PROD / 32;   // filter loader
+constexpr int MMA_WARP0 = B_WARP + 1;    // first of the MMA-issuing warps
+constexpr int N_THREADS = 768;     // 24 warps
+constexpr int EPI_WARP0 = 16;      // first of the eight epilogue warps (a multiple of 4: warp & 3 = TMEM lane quarter)
 constexpr int N_MMA_THREADS = 4;   // MMA issuers: one per Winograd position (its own accumulator columns)
 constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;
 
@@ -282,7 +284,7 @@ __device__ __forceinline__ void store16p(T *dst, const uint32_t (&pk)[8], int kb
 struct Smem {
   int raw_bytes, a_bytes, b_stage_bytes;   // one raw patch; one set of four slabs; one stage of four filter slabs
   int n_b_stages, n_a_bufs;
-  int off_raw[2], off_a[2], off_b, off_bars;
+  int off_raw[2], off_a[3], off_b, off_bars;
   int total;
 };
 
@@ -316,18 +318,18 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   const uint32_t raw0 = smem_u32(smem_raw_);
   const uint32_t base = (raw0 + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw_ + (base - raw0);
-  // barriers: raw_full[2] raw_empty[2] a_full[2] a_empty[2] b_full[8] b_empty[8] acc_full[2] acc_empty[2]
+  // barriers: raw_full[2] raw_empty[2] (4 unused) b_full[8] b_empty[8] acc_full[2] acc_empty[2] a_full[3] a_empty[3]
   const uint32_t bars = base + sl.off_bars;
   auto raw_full = [&](int i) { return bars + 8u * i; };
   auto raw_empty = [&](int i) { return bars + 8u * (2 + i); };
-  auto a_full = [&](int i) { return bars + 8u * (4 + i); };
-  auto a_empty = [&](int i) { return bars + 8u * (6 + i); };
+  auto a_full = [&](int i) { return bars + 8u * (28 + i); };
+  auto a_empty = [&](int i) { return bars + 8u * (31 + i); };
   auto b_full = [&](int i) { return bars + 8u * (8 + i); };
   auto b_empty = [&](int i) { return bars + 8u * (16 + i); };
   auto acc_full = [&](int i) { return bars + 8u * (24 + i); };
   auto acc_empty = [&](int i) { return bars + 8u * (26 + i); };
-  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(base_ptr + sl.off_bars + 256);
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + sl.off_bars + 260);
+  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(base_ptr + sl.off_bars + 512);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + sl.off_bars + 516);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef WINO_ROW_TRACE
@@ -337,10 +339,12 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     for (int i = 0; i < 2; ++i) {
       mbar_init(raw_full(i), 1);
       mbar_init(raw_empty(i), N_PROD / 32);                      // one arrival per producer warp
-      mbar_init(a_full(i), PAIR ? 2 * (N_PROD / 32) : N_PROD / 32);
-      mbar_init(a_empty(i), N_MMA_THREADS);                      // one commit per MMA-issuing thread
-      mbar_init(acc_full(i), N_MMA_THREADS);
+      mbar_init(acc_full(i), N_MMA_THREADS);                     // one commit per MMA-issuing thread
       mbar_init(acc_empty(i), PAIR ? 16 : 8);                    // one arrival per epilogue warp
+    }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(a_full(i), PAIR ? 2 * (N_PROD / 32) : N_PROD / 32);
+      mbar_init(a_empty(i), N_MMA_THREADS);
     }
     for (int i = 0; i < 8; ++i) {
       mbar_init(b_full(i), 1);
@@ -354,7 +358,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     __syncthreads();
     cluster_sync_all();
   }
-  if (warp == 10) {
+  if (warp == MMA_WARP0) {
     if (PAIR) {
       asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(512u) : "memory");
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
@@ -372,27 +376,52 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   const long long item0 = PAIR ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
   const long long item_step = PAIR ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
 
-  // item -> (n, od, rb, cb, nb); the channel block is the fastest index so consecutive CTAs share a patch
-  auto decode = [&](long long item, int &n, int &od, int &rb, int &cb, int &nb) {
-    nb = (int)(item % g.n_nblocks); item /= g.n_nblocks;
-    cb = (int)(item % g.n_cb); item /= g.n_cb;
-    rb = (int)(item % g.n_rb); item /= g.n_rb;
-    od = (int)(item % g.oD); item /= g.oD;
-    n = PAIR ? 2 * (int)item + (int)rank : (int)item;
+  // item -> (n, od, rb, cb, nb); the channel block is the fastest index so consecutive CTAs share a patch.  The roles
+  // that need the coordinates walk them as mixed-radix digits (first item and the stride are split once with
+  // divisions; every further item is five add-with-carry steps, not eight 64-bit divisions).
+  struct ItemWalk {
+    int nb, cb, rb, od, n5;          // digits of the current item (n5: image, or image pair)
+    int s_nb, s_cb, s_rb, s_od, s_n; // digits of the stride
+    int r_nb, r_cb, r_rb, r_od;      // radices
+    __device__ __forceinline__ void split(long long v, int &a, int &b, int &c, int &d, int &e) const {
+      a = (int)(v % r_nb); v /= r_nb;
+      b = (int)(v % r_cb); v /= r_cb;
+      c = (int)(v % r_rb); v /= r_rb;
+      d = (int)(v % r_od); v /= r_od;
+      e = (int)v;
+    }
+    __device__ __forceinline__ void init(long long first, long long step, int n_nb, int n_cb, int n_rb, int n_od) {
+      r_nb = n_nb; r_cb = n_cb; r_rb = n_rb; r_od = n_od;
+      split(first, nb, cb, rb, od, n5);
+      split(step, s_nb, s_cb, s_rb, s_od, s_n);
+    }
+    __device__ __forceinline__ void advance() {
+      int c;
+      nb += s_nb;     c = nb >= r_nb; nb -= c ? r_nb : 0;
+      cb += s_cb + c; c = cb >= r_cb; cb -= c ? r_cb : 0;
+      rb += s_rb + c; c = rb >= r_rb; rb -= c ? r_rb : 0;
+      od += s_od + c; c = od >= r_od; od -= c ? r_od : 0;
+      n5 += s_n + c;
+    }
+  };
+  auto make_walk = [&]() {
+    ItemWalk wk;
+    wk.init(item0, item_step, g.n_nblocks, g.n_cb, g.n_rb, g.oD);
+    return wk;
   };
   const int steps_per_item = g.kD * g.n_chunks;          // raw patches per item
   // When one channel block covers K and a whole item's filter slabs fit the stage ring, they are loaded once and
   // stay: stage index = slab position within the item, no refills.
-  const bool b_resident = !PAIR && g.n_nblocks == 1 && steps_per_item * g.PW * g.kH <= sl.n_b_stages;
+  const bool b_resident = g.n_nblocks == 1 && steps_per_item * g.PW * g.kH <= sl.n_b_stages;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- raw input patches
     {
       uint32_t it = 0;
       bool alive = true;
-      for (long long item = item0; item < g.n_items && alive; item += item_step) {
-        int n, od, rb, cb, nb;
-        decode(item, n, od, rb, cb, nb);
+      ItemWalk wk = make_walk();
+      for (long long item = item0; item < g.n_items && alive; item += item_step, wk.advance()) {
+        const int n = PAIR ? 2 * wk.n5 + (int)rank : wk.n5, od = wk.od, rb = wk.rb, cb = wk.cb;
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks; ++ch) {
             const int s = it & 1;
@@ -407,9 +436,9 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           }
       }
     }
-  } else if (warp <= 8) {
+  } else if (warp < B_WARP) {
     // ---------------------------------------------------------------- F(2,3) along W: raw patch -> four slabs
-    const int ptid = threadIdx.x - 32;                 // 0..255
+    const int ptid = threadIdx.x - 32;                 // 0..N_PROD-1
     const int v = ptid & 3;                            // 16-byte vector of the 32-channel slab
     const int n_tasks = g.slab_rows;                   // one task = one slab row (input row, column pair) x one vector
     uint32_t it_raw = 0, it_a = 0;
@@ -463,7 +492,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         ++it_raw;
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == B_WARP) {
     // ---------------------------------------------------------------- transformed-filter slabs
     {
       uint32_t it = 0;
@@ -472,9 +501,9 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       int s = 0;
       uint32_t s_par = 1u;                          // parity of the "stage is free" wait: first round passes
       uint32_t dst = base + sl.off_b;
-      for (long long item = item0; item < g.n_items && alive; item += item_step) {
-        int n, od, rb, cb, nb;
-        decode(item, n, od, rb, cb, nb);
+      ItemWalk wk = make_walk();
+      for (long long item = item0; item < g.n_items && alive; item += item_step, wk.advance()) {
+        const int nb = wk.nb;
         if (b_resident && item != item0) break;   // every slab of the filter is already in shared memory
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks && alive; ++ch)
@@ -508,13 +537,13 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         while (clock64() - start < 2000000LL) { }
       }
     }
-  } else if (warp >= 10 && warp < 10 + N_MMA_THREADS) {
+  } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + N_MMA_THREADS) {
     // ---------------------------------------------------------------- MMA issue (rank 0 of a pair issues for both CTAs)
     // Issuing one tcgen05.mma costs the thread about as long as an N = 128 MMA runs (~60 clocks), so whatever else
     // a single issuer does (barrier waits, commits, loop branches) is time the tensor pipe idles.  Four warps, one
     // per scheduler, each issue one of the four positions of every stage (their own accumulator columns); while
     // one waits or commits the others keep the pipe fed.
-    const int half = warp - 10;                        // position this warp issues
+    const int half = warp - MMA_WARP0;                 // position this warp issues
     if (rank == 0) {
 #define MMA_WAIT(bar_, par_, aw_, code_) mbar_wait(bar_, par_, aw_, code_)   /* every lane polls; lanes differ only when a wait gives up */
 #define MMA_ISSUE(d_, a_, b_, i_, acc_) do { if (PAIR) umma_f16_lohi_pair(d_, a_, b_, i_, acc_); else umma_f16_lohi(d_, a_, b_, i_, acc_); } while (0)   /* inside if (lane == 0) */
@@ -539,7 +568,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       const uint32_t b_lo_base = desc_lo(base + sl.off_b);
       uint32_t bs = 0, b_par = 0, b_lo0 = b_lo_base;
       const uint32_t n_a = (uint32_t)sl.n_a_bufs;
-      const uint32_t a_lo_buf0 = desc_lo(base + sl.off_a[0]), a_lo_buf1 = desc_lo(base + sl.off_a[1]);
+      const uint32_t a_lo_buf0 = desc_lo(base + sl.off_a[0]), a_lo_buf1 = desc_lo(base + sl.off_a[1]), a_lo_buf2 = desc_lo(base + sl.off_a[2]);
       uint32_t as = 0, a_par = 0;
       const uint32_t kh_step16 = (uint32_t)(g.CBW * 4);    // one filter row further = CBW slab rows of 64 bytes
       const int tail_chunk = (g.Cp - (g.n_chunks - 1) * KC > UMMA_K) ? -1 : g.n_chunks - 1;   // chunk with one K step only
@@ -569,11 +598,13 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             LAP(5);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) TL(9, it_a);
-            uint32_t a_lo_kh = (as ? a_lo_buf1 : a_lo_buf0) + a_half16;
-            for (int kh = 0; kh < kH; ++kh) {
+            uint32_t a_lo_kh = (as == 0 ? a_lo_buf0 : (as == 1 ? a_lo_buf1 : a_lo_buf2)) + a_half16;
+            // one stage = one filter row kh: straight-line code for the usual three rows (a taken branch costs this
+            // lone warp ~100 clocks of instruction fetch)
+            auto do_stage = [&]() -> bool {
               LAP(0);
               if (!(b_resident && n_done > 0))
-                if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) { alive = false; break; }
+                if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) return false;
               LAP(1); if (lane == 0) TL(0, it_b);
               if (!skip_mma && lane == 0) {
 #pragma unroll
@@ -594,6 +625,13 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
               b_lo0 += b_stage16;
               if (++bs == b_ring) { bs = 0; b_lo0 = b_lo_base; b_par = b_resident ? 0u : (b_par ^ 1u); }
               LAP(2);
+              return true;
+            };
+            if (kH == 3) {
+              if (!do_stage() || !do_stage() || !do_stage()) { alive = false; break; }
+            } else {
+              for (int kh = 0; kh < kH && alive; ++kh) alive = do_stage();
+              if (!alive) break;
             }
             LAP(8);
             MMA_COMMIT(a_empty((int)as));
@@ -633,9 +671,9 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     constexpr int C_PER_WARP = BN / 2;
     uint32_t n_done = 0;
     bool alive = true;
-    for (long long item = item0; item < g.n_items && alive; item += item_step, ++n_done) {
-      int n, od, rb, cb, nb;
-      decode(item, n, od, rb, cb, nb);
+    ItemWalk wk = make_walk();
+    for (long long item = item0; item < g.n_items && alive; item += item_step, ++n_done, wk.advance()) {
+      const int n = PAIR ? 2 * wk.n5 + (int)rank : wk.n5, od = wk.od, rb = wk.rb, cb = wk.cb, nb = wk.nb;
       const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
       const uint32_t use = (ACC_BUFS == 2) ? (n_done >> 1) : n_done;
       unsigned got = 0;
@@ -734,7 +772,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     g_row_trace[15] += (unsigned long long)((g.n_items + gridDim.x - 1) / gridDim.x);
   }
 #endif
-  if (warp == 10) {
+  if (warp == MMA_WARP0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
@@ -843,11 +881,11 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   p.slabs = d.kD * d.kH * p.PW * 4;
   p.filter_elems = (long long)p.slabs * d.K * Cp;
   // CTA pairs: the two SMs of a cluster take images 2n and 2n + 1 of one item and share every filter slab (each loads
-  // half of it), which halves the filter bytes an SM pulls per multiply-add.  Used when the slabs are streamed (more
-  // than one channel block, or an item's slabs do not fit the stage ring) and the accumulator is 128 channels wide.
+  // half of it).  One M = 256 MMA then covers both tile blocks in the time of an M = 128 one whenever the instruction
+  // floor (~60 clocks) binds, i.e. at N = 64 it doubles the MMA rate; at N = 128 it halves the filter bytes an SM
+  // pulls per multiply-add and leaves room for twice as many stages.  Used whenever the batch has two images.
   static const int pair_env = [] { const char *v = getenv("WINOCONV_ROW_PAIR"); return v && *v ? atoi(v) : -1; }();
-  p.pair = (pair_env != 0 && p.BN == 128 && p.MB == 1 && d.N >= 2 &&
-            (p.n_nblocks > 1 || p.n_chunks * d.kD * d.kH * p.PW > 6)) ? 1 : 0;
+  p.pair = (pair_env != 0 && p.MB == 1 && d.N >= 2) ? 1 : 0;
   p.n_items = (long long)(p.pair ? (d.N + 1) / 2 : d.N) * d.oD * p.n_rb * p.n_cb * p.n_nblocks;
   if (p.patch_w > 256 || p.patch_h > 256) return false;
   // shared memory: 2 raw patches, 2 slab sets (1 if two do not leave room for 3 filter stages), then as many
@@ -856,9 +894,18 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   const int a_bytes = ((4 * p.slab_rows * 64 + 1023) / 1024) * 1024;
   const int b_stage = 4 * (p.pair ? p.BN / 2 : p.BN) * 64;
   const int budget = 227 * 1024;
-  int n_a = 2;
+  // three slab sets when three filter stages still fit beside them (CTA pairs: half-size stages): the producers then
+  // run a full 32-channel step ahead of the MMAs instead of racing the step in flight (measured on the 256- and
+  // 512-channel VGG layers: 0.65 ms against 0.69 ms with two sets and eight stages)
+  static const int na_env = [] { const char *v = getenv("WINOCONV_ROW_ABUFS"); return v && *v ? atoi(v) : 0; }();
+  int n_a = (na_env >= 1 && na_env <= 3) ? na_env : 3;
   int fixed = 2 * raw_bytes + n_a * a_bytes + 1024 /*bars*/ + 1024 /*align*/;
-  if ((budget - fixed) / b_stage < 3) {
+  static const int minb_env = [] { const char *v = getenv("WINOCONV_ROW_MINB"); return v && *v ? atoi(v) : 3; }();
+  if (n_a == 3 && (budget - fixed) / b_stage < minb_env) {
+    n_a = 2;
+    fixed = 2 * raw_bytes + n_a * a_bytes + 2048;
+  }
+  if (n_a == 2 && (budget - fixed) / b_stage < 3) {
     n_a = 1;
     fixed = 2 * raw_bytes + n_a * a_bytes + 2048;
   }
@@ -901,7 +948,9 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   sl.raw_bytes = p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
   sl.a_bytes = p.a_bytes; sl.b_stage_bytes = p.b_stage_bytes; sl.n_b_stages = p.n_b_stages;
   sl.n_a_bufs = p.n_a_bufs;
-  sl.off_a[0] = 0; sl.off_a[1] = p.n_a_bufs == 2 ? p.a_bytes : 0;  // slabs first: 1024-byte aligned
+  sl.off_a[0] = 0;                                                 // slabs first: 1024-byte aligned
+  sl.off_a[1] = p.n_a_bufs >= 2 ? p.a_bytes : 0;
+  sl.off_a[2] = p.n_a_bufs >= 3 ? 2 * p.a_bytes : 0;
   sl.off_b = p.n_a_bufs * p.a_bytes;                               // filter stages: multiples of 1024
   sl.off_raw[0] = sl.off_b + p.n_b_stages * p.b_stage_bytes;
   sl.off_raw[1] = sl.off_raw[0] + p.raw_bytes;
@@ -984,7 +1033,8 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((m_rows >> 4) << 24);
 #define ROWF_DISPATCH(T)                                                                                         \
   do {                                                                                                           \
-    if (p.pair) return launch_rf<T, 128, 1, true>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);            \
+    if (p.pair) return p.BN == 64 ? launch_rf<T, 64, 1, true>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail) \
+                                  : launch_rf<T, 128, 1, true>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail); \
     if (p.MB == 2) return launch_rf<T, 64, 2, false>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);         \
     return p.BN == 64 ? launch_rf<T, 64, 1, false>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail)            \
                       : launch_rf<T, 128, 1, false>(d, p, mx, mu, y, bias, sm_count, idesc, s, detail);          \
