@@ -77,6 +77,10 @@ ROW_CASES = [c for c in SMALL + FUSED_EXTRA if c[5] == 1 and c[7] != 4 and c[4][
     (2, 96, 192, (14, 14), (3, 3), 1, 1, 2),       # 16 x 8 block shape, two channel blocks, slab tail
     (1, 40, 72, (9, 50), (3, 3), 1, 0, 2),         # no padding, K not a block multiple
     (1, 16, 16, (12, 12), (7, 7), 1, 3, 2),        # tallest kernel the row kernel takes
+    (3, 64, 128, (20, 36), (3, 3), 1, 1, 2),       # CTA pairs, odd batch: the last pair holds one image
+    (5, 24, 64, (17, 23), (3, 3), 1, 1, 2),        # CTA pairs at 64-wide accumulators (two TMEM buffers), odd batch
+    (4, 256, 256, (28, 28), (3, 3), 1, 1, 2),      # eight channel slabs, filter slabs streamed through the ring
+    (2, 512, 128, (14, 14), (3, 3), 1, 1, 2),      # sixteen channel slabs, one channel block
 ]
 
 
@@ -92,8 +96,8 @@ def test_row_piece_cases(n, c, k, sp, ks, stride, pad, m, dtype):
 
 
 def test_row_piece_epilogue_bias_relu_pool():
-    for hw in ((13, 14), (32, 64), (16, 16)):
-        x = seeded((2, 16) + hw, 31, dtype=torch.float16)
+    for nb, hw in ((2, (13, 14)), (2, (32, 64)), (2, (16, 16)), (3, (16, 24)), (1, (16, 24))):
+        x = seeded((nb, 16) + hw, 31, dtype=torch.float16)
         w = wo.kaiming_normal((72, 16, 3, 3), 32).half()
         b = seeded((72,), 33, dtype=torch.float16)
         o = wo.direct_conv_f64(x, w, padding=1) + b.double().view(1, -1, 1, 1)
