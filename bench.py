@@ -42,9 +42,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
 # summarised under profiles/ (None until a capture exists for that kernel and workload).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    # rowfused_kernel, C = K = 256 at 56 x 56 (VGG layers 6-7): 365.5 MB at N = 128 in the capture of
-    # profiles/rowfused_c256_k256_56_ncu.md, scaled to the bench's N = 256 (traffic is proportional to N)
-    ("vgg16", "rowfused_kernel"): 731.0e6,
+    # rowfused_kernel, C = K = 256 at 56 x 56 (VGG layers 6-7): 169.1 MB at N = 64 in the capture of
+    # profiles/rowfused_pair_c256_k256_56_ncu.md, scaled to the bench's N = 256 (traffic is proportional to N;
+    # algorithmic bytes of that layer at N = 256: 824 MB, part of y is still dirty in L2 when the kernel ends)
+    ("vgg16", "rowfused_kernel"): 676.4e6,
 }
 
 
@@ -409,7 +410,8 @@ def run_ours(args):
     dom = max(range(3), key=lambda i: stage_tot[i])
     is_fused = all(c.info.algo in (capi.ALGO_FUSED, capi.ALGO_ROW) for c in layers)
     is_row = all(c.info.algo == capi.ALGO_ROW for c in layers)
-    n_dom_launch = sum(l["launches"] if is_fused else l["launches"] // 3 for l in per_layer)
+    # fused paths: one dominant-kernel launch per layer (layer 1 adds a small channel-padding launch, timed with it)
+    n_dom_launch = len(per_layer) if is_fused else sum(l["launches"] // 3 for l in per_layer)
     esz = 2
     if dom == 1:
         alg = sum(c.info.gemm_flops for c in layers)

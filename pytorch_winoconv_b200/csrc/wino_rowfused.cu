@@ -101,7 +101,11 @@ __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile unsigned *abort_word, unsigned code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
+  unsigned polls = 0;
   while (!mbar_try_wait(bar, parity)) {
+    // the abort word and the clock are looked at every 32nd failed poll: twenty waiting warps that read shared
+    // memory on every poll take load/store slots from the producers
+    if ((++polls & 31u) != 0u) continue;
     if (*abort_word != 0u) return false;
     if (clock64() - start > WAIT_LIMIT_CLOCKS) {
       *abort_word = code;
