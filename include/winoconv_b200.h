@@ -76,7 +76,9 @@ typedef struct winoconv_desc {
   int32_t ker_size[3];   /* kD, kH, kW (each 1..10);  kD = 1 if ndim = 2                     */
   int32_t stride[3];     /* 1 or 2 per dimension                                             */
   int32_t pad[3];        /* symmetric zero padding per dimension, applied in-kernel          */
-  int32_t tile_m;        /* Winograd output block: 0 = auto, 2 = F(2,r), 4 = F(4x4,3x3)      */
+  int32_t tile_m;        /* Winograd output block: 0 = auto (2 where a single-kernel path
+                          * takes the layer, else 4 for 2-D 3x3 stride 1), 2 = F(2,r),
+                          * 4 = F(4x4,3x3)                                               */
   int32_t dtype;         /* winoconv_dtype_t of x, weights, y and of the transformed filter  */
   int32_t weight_layout; /* winoconv_wlayout_t                                               */
   uint32_t epilogue;     /* WINOCONV_EPI_* bits                                              */
@@ -142,12 +144,17 @@ WINOCONV_API int winoconv_plan_pieces(const winoconv_desc_t *desc, int32_t *piec
 WINOCONV_API int winoconv_filter_transform(const winoconv_desc_t *desc, const void *weights, void *u, void *stream);
 
 /*
- * y = conv(x, w): input transform (B^T d B with in-kernel zero padding, DWM piece offsets and
- * stride-2 polyphase addressing) -> one GEMM per Winograd position -> output transform
- * (A^T m A, summed over pieces in registers, bias / ReLU / 2x2 max-pool epilogue, one store per
- * output element).  Tiles are processed in blocks sized to the scratch given, so V and M stay
- * cache resident: v_ws holds [positions][block][c_pad] in desc->dtype, m_ws holds
- * [positions][block][K] in desc->product_dtype.
+ * y = conv(x, w) by the algorithm the plan names (winoconv_plan_info_t.algo):
+ *   ROW / FUSED  one kernel: input tiles are transformed in shared memory, multiplied on the tensor
+ *                cores with the DWM pieces summed in the accumulator, and written through the output
+ *                transform with the bias / ReLU / 2x2 max-pool epilogue; v_ws and m_ws are not used
+ *                (ROW pads C to a multiple of 8 into v_ws when it is not one already).
+ *   STAGED       input transform (B^T d B with in-kernel zero padding, DWM piece offsets and stride-2
+ *                polyphase addressing) -> one GEMM per Winograd position -> output transform (A^T m A,
+ *                summed over pieces in registers, same epilogue, one store per output element).  Tiles
+ *                are processed in blocks sized to the scratch given: v_ws holds
+ *                [positions][block][c_pad] in desc->dtype, m_ws [positions][block][K] in
+ *                desc->product_dtype.
  * Replaces DWM<T> (src/winograd_conv.cpp:16-127; bound at pybind/bind.cpp:23) and everything it
  * launches: inputNorm2WinoTransform, forwardAssign, cublasSgemmBatched / cublasHgemmBatched,
  * outputWino2NormTransform, outputAggregate (src/base_conv_launchers.cu:282-399,
