@@ -1,0 +1,148 @@
+"""``torch.nn`` modules over the engine: the caller layer of the forward path.
+
+The reference patches a copy of torch's ``conv.py`` so that ``Conv2d`` / ``Conv3d`` send large stride-1
+kernels to ``dwm.dwm2d`` / ``dwm.dwm3d`` (or ``matrix_conv.conv16``) in half precision and everything
+else to cuDNN (reference: ``conv.py:324-340`` and ``conv.py:465-481``).  These classes keep that
+interface -- same constructor as ``torch.nn.Conv2d`` / ``Conv3d``, same parameters and ``state_dict``,
+half-precision compute by default -- and run *every* supported shape on the engine: 3x3 kernels and
+stride 2 included, no cuDNN branch.  What the reference pays per call and these do not:
+
+* the filter transform: U = G g G^T is cached and recomputed only when the weight tensor changes
+  (its version counter, storage, dtype or device), not on every forward;
+* the layout copies of ``dwm.py:129-133,144``: an input in ``torch.channels_last`` (``channels_last_3d``)
+  memory format is handed to the kernels as it lies, and the result comes back as an NCHW-shaped
+  view of the channels-last buffer the kernels wrote (any other input is copied once);
+* separate bias / ReLU / max-pool passes: ``activation="relu"`` and ``pool=2`` run in the
+  convolution's epilogue.
+
+Forward only, as upstream: a call that would need a gradient raises.  ``groups != 1`` and dilation
+raise too (the reference accepts ``groups`` and silently computes groups = 1).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import capi, engine
+
+__all__ = ["Conv2d", "Conv3d"]
+
+
+class _WinoConvMixin:
+    """Shared forward of :class:`Conv2d` and :class:`Conv3d` (``self`` is a ``torch.nn._ConvNd``)."""
+
+    _nd: int = 2
+
+    def _init_wino(self, compute_dtype, activation, pool, tile_m, algo):
+        if activation not in (None, "relu"):
+            raise ValueError("activation must be None or 'relu'")
+        if pool not in (None, 1, 2):
+            raise ValueError("pool must be None or 2 (2x2 max-pool fused into the epilogue)")
+        if any(int(d) != 1 for d in self.dilation):
+            raise NotImplementedError("dilated convolution is not a Winograd / DWM case")
+        if self.groups != 1:
+            raise NotImplementedError("groups != 1 is not supported (the reference ignores the argument)")
+        if self.padding_mode != "zeros" or isinstance(self.padding, str):
+            raise NotImplementedError("only explicit zero padding")
+        self.compute_dtype = compute_dtype
+        self.activation = activation
+        self.pool = 2 if pool == 2 else None
+        self.tile_m = int(tile_m)
+        self.algo = int(algo)
+        self._plans = {}          # (input shape, dtype, device) -> engine.WinoConv
+        self._weight_key = None   # identity of the weight the cached plans were built from
+
+    # -- cache -------------------------------------------------------------------------------------
+    def _current_weight_key(self, dtype, device):
+        w, b = self.weight, self.bias
+        return (w.data_ptr(), w._version, None if b is None else (b.data_ptr(), b._version), dtype, device)
+
+    def _plan_for(self, in_shape_cl: Tuple[int, ...], dtype, device) -> engine.WinoConv:
+        key = self._current_weight_key(dtype, device)
+        if key != self._weight_key:            # the parameters changed: every cached filter transform is stale
+            self._plans.clear()
+            self._weight_key = key
+        plan = self._plans.get(in_shape_cl)
+        if plan is None:
+            w = self.weight.detach().to(device=device, dtype=dtype)
+            b = None if self.bias is None else self.bias.detach().to(device=device, dtype=dtype)
+            plan = engine.WinoConv(in_shape_cl, w, stride=tuple(int(s) for s in self.stride),
+                                   padding=tuple(int(p) for p in self.padding), tile_m=self.tile_m, bias=b,
+                                   relu=self.activation == "relu", pool2=self.pool == 2, algo=self.algo)
+            self._plans[in_shape_cl] = plan
+        return plan
+
+    # -- forward -----------------------------------------------------------------------------------
+    def forward(self, input: torch.Tensor) -> torch.Tensor:      # noqa: A002  (torch's argument name)
+        nd = self._nd
+        if input.dim() != nd + 2:
+            raise ValueError(f"expected a {nd + 2}-D input [N, C, {'D, ' if nd == 3 else ''}H, W]")
+        if not input.is_cuda:
+            raise RuntimeError("the Winograd engine runs on CUDA devices only: there is no CPU or cuDNN path")
+        if torch.is_grad_enabled() and (input.requires_grad or self.weight.requires_grad and self.training):
+            raise NotImplementedError("forward only: call under torch.no_grad() / module.eval() "
+                                      "(the reference has no backward pass either)")
+        dtype = self.compute_dtype if self.compute_dtype is not None else input.dtype
+        x = input.detach()
+        if x.dtype != dtype:
+            x = x.to(dtype)
+        # channels-last view of the input: free when the tensor already lies that way
+        perm_in = (0, *range(2, 2 + nd), 1)
+        x_cl = x.permute(*perm_in)
+        if not x_cl.is_contiguous():
+            x_cl = x_cl.contiguous()
+        plan = self._plan_for(tuple(int(s) for s in x_cl.shape), dtype, x.device)
+        y_cl = plan(x_cl)
+        # NCHW-shaped view of the channels-last result (torch.channels_last memory format): no copy
+        return y_cl.permute(0, nd + 1, *range(1, nd + 1))
+
+    def extra_repr(self) -> str:
+        s = super().extra_repr()
+        s += f", compute_dtype={self.compute_dtype}"
+        if self.activation:
+            s += f", activation={self.activation}"
+        if self.pool:
+            s += f", pool={self.pool}"
+        return s
+
+    @property
+    def planned_algorithms(self):
+        """Algorithm the engine chose for every input shape seen so far: {shape: 'row' | 'fused' | 'staged'}."""
+        names = {capi.ALGO_ROW: "row", capi.ALGO_FUSED: "fused", capi.ALGO_STAGED: "staged"}
+        return {shape: names.get(int(p.info.algo), str(p.info.algo)) for shape, p in self._plans.items()}
+
+
+class Conv2d(_WinoConvMixin, nn.Conv2d):
+    """``torch.nn.Conv2d`` whose forward is the Winograd / DWM engine (reference: ``conv.py:305-340``).
+
+    Extra keyword arguments: ``compute_dtype`` (default ``torch.float16`` as upstream, ``None`` keeps the
+    input's dtype; fp32 runs the fp32-accumulate SIMT path), ``activation`` (``None`` / ``"relu"``),
+    ``pool`` (``None`` / ``2``), ``tile_m`` (0 auto, 2, 4) and ``algo`` (``capi.ALGO_*``).
+    """
+
+    _nd = 2
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True,
+                 padding_mode="zeros", device=None, dtype=None, *, compute_dtype: Optional[torch.dtype] = torch.float16,
+                 activation: Optional[str] = None, pool: Optional[int] = None, tile_m: int = 0,
+                 algo: int = capi.ALGO_AUTO):
+        nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias,
+                           padding_mode, device=device, dtype=dtype)
+        self._init_wino(compute_dtype, activation, pool, tile_m, algo)
+
+
+class Conv3d(_WinoConvMixin, nn.Conv3d):
+    """``torch.nn.Conv3d`` on the engine (reference: ``conv.py:446-481``); arguments as :class:`Conv2d`.
+    The 2x2 pool of the epilogue acts on H and W."""
+
+    _nd = 3
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True,
+                 padding_mode="zeros", device=None, dtype=None, *, compute_dtype: Optional[torch.dtype] = torch.float16,
+                 activation: Optional[str] = None, pool: Optional[int] = None, tile_m: int = 0,
+                 algo: int = capi.ALGO_AUTO):
+        nn.Conv3d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias,
+                           padding_mode, device=device, dtype=dtype)
+        self._init_wino(compute_dtype, activation, pool, tile_m, algo)

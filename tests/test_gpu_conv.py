@@ -163,7 +163,7 @@ def test_blocked_passes_equal_single_pass():
     w = wo.kaiming_normal((16, 16, 3, 3), 42).half()
     dev = torch.device("cuda", 0)
     xl = x.permute(0, 2, 3, 1).contiguous().to(dev)
-    conv = engine.WinoConv(xl.shape, w.to(dev), padding=1)      # F(4x4,3x3): staged
+    conv = engine.WinoConv(xl.shape, w.to(dev), padding=1, tile_m=4)      # F(4x4,3x3): staged
     y_full = conv(xl).clone()
     v = torch.empty(int(conv.info.input_ws_bytes_min) * 2, dtype=torch.uint8, device=dev)
     m = torch.empty(int(conv.info.product_ws_bytes_min) * 2, dtype=torch.uint8, device=dev)
@@ -236,8 +236,14 @@ def test_auto_resolves_to_fused_for_16bit_f2_and_staged_otherwise():
     w3 = wo.kaiming_normal((8, 8, 3, 3), 3).half()
     assert run_engine(x, w5, padding=2)[1].info.algo == capi.ALGO_ROW
     assert run_engine(x, w5, padding=2, stride=2)[1].info.algo == capi.ALGO_FUSED   # stride 2: 3x3 pieces
-    assert run_engine(x, w3, padding=1)[1].info.algo == capi.ALGO_STAGED          # auto tile_m = 4
+    assert run_engine(x, w3, padding=1)[1].info.algo == capi.ALGO_ROW             # 16-bit: 2-wide tiles, one kernel
     assert run_engine(x, w3, padding=1, tile_m=2)[1].info.algo == capi.ALGO_ROW
+    c4 = run_engine(x, w3, padding=1, tile_m=4)[1]                                # F(4x4,3x3) on request: staged
+    assert c4.info.algo == capi.ALGO_STAGED and c4.info.positions == 36
+    cs = run_engine(x, w3, padding=1, algo=capi.ALGO_STAGED)[1]                   # staged on request: auto tile is 4
+    assert cs.info.algo == capi.ALGO_STAGED and cs.info.positions == 36
+    c32 = run_engine(x.float(), w3.float(), padding=1)[1]                         # fp32: staged F(4x4,3x3)
+    assert c32.info.algo == capi.ALGO_STAGED and c32.info.positions == 36
     assert run_engine(x.float(), w3.float(), padding=1, tile_m=2)[1].info.algo == capi.ALGO_STAGED
 
 

@@ -43,4 +43,23 @@ def test_vgg16_stack_matches_float64_stack():
     stack.capture(xl)
     yg = stack.replay(xl).permute(0, 3, 1, 2).float().cpu()
     assert torch.equal(yg, y)
+    # default path: one row-piece kernel per layer (+ the channel padding of layer 1)
+    assert all(c.info.algo == capi.ALGO_ROW for c in stack.layers) and stack.launches_per_call == 14
+
+
+def test_vgg16_stack_staged_f43_matches_float64_stack():
+    """The same stack through input transform -> GEMM -> output transform with F(4x4,3x3) tiles."""
+    batch = 2
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(batch, 3, 224, 224, generator=g).half()
+    ws = _weights(torch.float16)
+    stack = engine.VGG16ConvStack([w.cuda() for w in ws], batch, tile_m=4, algo=capi.ALGO_STAGED)
+    xl = x.permute(0, 2, 3, 1).contiguous().cuda()
+    y = stack(xl).permute(0, 3, 1, 2).float().cpu()
+    torch.cuda.synchronize()
+    assert capi.read_device_error() == 0
+    assert all(c.info.algo == capi.ALGO_STAGED and c.info.positions == 36 for c in stack.layers)
     assert stack.launches_per_call >= 39
+    err = wo.error_metrics(y, wo.vgg16_conv_stack_f64(x, ws))
+    print("vgg16 staged F(4,3) stack error vs float64", err)
+    assert err["E_A"] < 3e-2, err

@@ -37,7 +37,7 @@ def _both(x, conv):
 
 def test_static_scratch_forward_matches_on_consecutive_calls():
     # layer A needs several passes through the 32 MiB array; layer B is a different shape and dtype
-    xa, ca = _layer(1, 16, 64, 96, 56, 3, 1, torch.float16)
+    xa, ca = _layer(1, 16, 64, 96, 56, 3, 1, torch.float16, tile_m=4)     # F(4x4,3x3): the staged flow, which needs scratch
     xb, cb = _layer(2, 2, 24, 40, 21, 5, 2, torch.float32)
     assert ca.info.algo == capi.ALGO_STAGED and cb.info.algo == capi.ALGO_STAGED
     need_a = int(ca.info.tiles) * (int(ca.info.input_ws_bytes_min) + int(ca.info.product_ws_bytes_min)) // 128
