@@ -292,6 +292,13 @@ struct Smem {
   int total;
 };
 
+// Timing ablations exist in development builds only; in the shipped library every switch is the constant false.
+#ifdef WINO_ROW_TRACE
+#define ROW_DBG(g_, bit_) (((g_).dbg & (bit_)) != 0u)
+#else
+#define ROW_DBG(g_, bit_) false
+#endif
+
 struct RGeom {
   int N, C, K;
   int Cp;                 // channels of the (padded) input the TMA map addresses
@@ -307,7 +314,7 @@ struct RGeom {
   int n_nblocks;
   long long n_items;
   unsigned epilogue;
-  unsigned dbg;           // timing experiments only (WINOCONV_ROW_DBG): 1 no filter TMA, 2 no input TMA, 4 no transform, 8 no MMA, 16 no stores
+  unsigned dbg;           // development builds only (WINO_ROW_TRACE): 2 no input TMA, 4 no transform, 8 no MMA, 16 no stores
 };
 
 template <typename T, int BN, int MB, bool PAIR>
@@ -430,7 +437,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           for (int ch = 0; ch < g.n_chunks; ++ch) {
             const int s = it & 1;
             if (!mbar_wait_warp(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
-            if (g.dbg & 2u) { if (lane == 0) mbar_arrive(raw_full(s)); ++it; continue; }
+            if (ROW_DBG(g, 2u)) { if (lane == 0) mbar_arrive(raw_full(s)); ++it; continue; }
             if (lane == 0) {
               mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
               tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
@@ -468,7 +475,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           if (ptid == 0) TL(4, it_a);
           uint8_t *slab = base_ptr + sl.off_a[as];
           const int slab_bytes = g.slab_rows * 64;
-          for (int row = ptid >> 2; row < ((g.dbg & 4u) ? 0 : n_tasks); row += N_PROD / 4) {
+          for (int row = ptid >> 2; row < (ROW_DBG(g, 4u) ? 0 : n_tasks); row += N_PROD / 4) {
             const int ir = row >> cbw_shift, cp = row - (ir << cbw_shift);
             const uint8_t *src = raw + ((size_t)(ir * g.patch_w + 2 * cp + 3 * w) * KC + v * 8) * 2;
             V8<T> d0, d1, d2, d3;
@@ -578,7 +585,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       const int tail_chunk = (g.Cp - (g.n_chunks - 1) * KC > UMMA_K) ? -1 : g.n_chunks - 1;   // chunk with one K step only
       const int kH = g.kH, PW = g.PW, n_chunks = g.n_chunks;   // loop bounds in registers
       const long long n_items = g.n_items;
-      const bool skip_mma = (g.dbg & 8u) != 0;
+      const bool skip_mma = ROW_DBG(g, 8u);
       const uint32_t a_half16 = (uint32_t)half * slab16, b_half16 = (uint32_t)half * B_SLAB16;
       for (long long item = item0; item < n_items && alive; item += item_step, ++n_done) {
         const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
@@ -670,7 +677,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     const bool pool = (g.epilogue & WINOCONV_EPI_POOL2) != 0;
     // widest store the output allows: 32 bytes (K % 16, 32-byte aligned base), 16 bytes (K % 8), or elements
     const int st_mode = ((g.K % 16) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0) ? 2 : ((g.K % 8) == 0 ? 1 : 0);
-    const bool no_store = (g.dbg & 16u) != 0;
+    const bool no_store = ROW_DBG(g, 16u);
     const int K = g.K;
     constexpr int C_PER_WARP = BN / 2;
     uint32_t n_done = 0;
@@ -946,8 +953,12 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   g.PW = p.PW; g.RB = p.RB; g.CBW = p.CBW; g.MB = p.MB; g.n_rb = p.n_rb; g.n_cb = p.n_cb; g.slab_rows = p.slab_rows;
   g.patch_h = p.patch_h; g.patch_w = p.patch_w; g.n_chunks = p.n_chunks; g.n_nblocks = p.n_nblocks;
   g.n_items = p.n_items; g.epilogue = d.epilogue;
+#ifdef WINO_ROW_TRACE
   static const unsigned dbg = [] { const char *v = getenv("WINOCONV_ROW_DBG"); return v && *v ? (unsigned)atoi(v) : 0u; }();
   g.dbg = dbg;
+#else
+  g.dbg = 0u;
+#endif
   Smem sl;
   sl.raw_bytes = p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
   sl.a_bytes = p.a_bytes; sl.b_stage_bytes = p.b_stage_bytes; sl.n_b_stages = p.n_b_stages;
