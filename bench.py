@@ -81,25 +81,106 @@ def parse_args():
 # clocks: sample nvidia-smi while the timed regions run
 # ---------------------------------------------------------------------------------------------------
 class ClockSampler:
+    """SM clock, power and throttle reasons of one GPU, sampled while the timed regions run.
+
+    Reads NVML from a thread of this process every few milliseconds (the timed regions of the default run
+    last ~0.1 s, shorter than nvidia-smi's start-up); falls back to an `nvidia-smi -lms` child when the NVML
+    module is missing.  Only samples taken inside a `with sampler.window():` block enter the summary.
+    Reading only: no clock, power or mode setting is touched.
+    """
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, gpu_index):
-        self.proc = None
-        self.path = os.path.join(ROOT, "gpurun_out", f"bench_clocks_{gpu_index}.csv")
         self.gpu = gpu_index
+        self.path = os.path.join(ROOT, "gpurun_out", f"bench_clocks_{gpu_index}.csv")
+        self.proc = None
+        self.thread = None
+        self.samples = []        # (t, sm_mhz, power_w, reason bitmask)
+        self.windows = []        # (t0, t1)
+        self.sm_max = None
+        self._stop = False
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
 
     def start(self):
+        os.makedirs(os.path.dirname(self.path), exist_ok=True)
         try:
-            os.makedirs(os.path.dirname(self.path), exist_ok=True)
+            pynvml, h = self._nvml_handle()
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+
+            def loop():
+                while not self._stop:
+                    try:
+                        sm = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                        pw = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
+                        rs = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                        self.samples.append((time.perf_counter(), sm, pw, rs))
+                    except Exception:
+                        pass
+                    time.sleep(0.003)
+
+            import threading
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
             self.fh = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
                                           "-lms", "25", "-i", str(self.gpu)], stdout=self.fh, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
+    class _Window:
+        def __init__(self, owner):
+            self.owner = owner
+
+        def __enter__(self):
+            self.t0 = time.perf_counter()
+
+        def __exit__(self, *exc):
+            self.owner.windows.append((self.t0, time.perf_counter()))
+            return False
+
+    def window(self):
+        return ClockSampler._Window(self)
+
     def stop(self):
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            inside = [s for s in self.samples if any(t0 <= s[0] <= t1 for t0, t1 in self.windows)]
+            used = inside if inside else self.samples
+            try:
+                with open(self.path, "w") as fh:
+                    fh.write("t_s,sm_mhz,power_w,reasons_mask,in_timed_region\n")
+                    for smp in self.samples:
+                        fh.write("%.6f,%.0f,%.1f,0x%x,%d\n" % (smp[0], smp[1], smp[2], smp[3], int(smp in inside)))
+            except Exception:
+                pass
+            if not used:
+                return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": ["no samples"]}
+            mask = 0
+            for smp in used:
+                mask |= smp[3]
+            reasons = sorted(n for n, bit in self.REASON_BITS.items() if mask & bit)
+            return {"sm_mhz": statistics.median(s[1] for s in used), "sm_max_mhz": self.sm_max, "reasons": reasons,
+                    "power_w_max": max(s[2] for s in used), "samples": len(used),
+                    "sampled": "NVML every ~3 ms inside the timed regions" if inside else "NVML, whole run"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -124,7 +205,7 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "power_w_max": max(power), "samples": len(sm)}
+                "power_w_max": max(power), "samples": len(sm), "sampled": "nvidia-smi -lms 25, whole run"}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -314,11 +395,12 @@ def run_ours(args):
         step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
+    with sampler.window():
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
     ms_local = e0.elapsed_time(e1)
     ms = sharding.max_over_ranks(ms_local)
     total_images = sharding.sum_over_ranks(batch)
@@ -373,10 +455,11 @@ def run_ours(args):
     run_e2e(3)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    run_e2e(args.steps)
-    f1.record()
-    barrier()
+    with sampler.window():
+        f0.record()
+        run_e2e(args.steps)
+        f1.record()
+        barrier()
     ms_e2e = sharding.max_over_ranks(f0.elapsed_time(f1))
     e2e_value = total_images * args.steps / (ms_e2e / 1e3)
     clocks = sampler.stop()

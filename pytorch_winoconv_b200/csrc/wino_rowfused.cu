@@ -29,6 +29,9 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "wino_common.cuh"
 #include "wino_launch.h"
@@ -945,8 +948,24 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
                              const void *bias, int sm_count, uint32_t idesc, cudaStream_t s, const char **detail) {
   using namespace rowf;
   auto kern = rowfused_kernel<T, BN, MB, PAIR>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_total);
-  if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
+  // Per device and kernel instance, remembered across calls (an eager caller pays these host calls per layer):
+  // the largest dynamic shared memory size set so far, and how many CTA pairs can be resident at once.
+  static std::mutex cache_mutex;
+  static std::map<int, std::pair<int, int>> cache;   // device -> (smem attribute set, resident clusters or 0)
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { *detail = "cudaGetDevice failed"; return e; }
+  int known_clusters = 0;
+  {
+    std::lock_guard<std::mutex> lock(cache_mutex);
+    std::pair<int, int> &c = cache[dev];
+    if (c.first < p.smem_total) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_total);
+      if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
+      c.first = p.smem_total;
+    }
+    known_clusters = c.second;
+  }
   RGeom g;
   g.N = d.N; g.C = d.C; g.K = d.K; g.Cp = p.Cp; g.D = d.D; g.H = d.H; g.W = d.W; g.oD = d.oD; g.oH = d.oH; g.oW = d.oW;
   g.yH = d.yH; g.yW = d.yW; g.pD = d.pD; g.pH = d.pH; g.pW = d.pW; g.kD = d.kD; g.kH = d.kH; g.kW = d.kW;
@@ -985,9 +1004,12 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
     cfg.numAttrs = 1;
     // one resident pair per two SMs where the GPCs allow it; fewer pairs when they do not (the items are strided over
     // the pairs launched, so every launched pair must be resident)
-    int max_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0 && max_clusters < pairs)
-      cfg.gridDim = dim3((unsigned)(2 * max_clusters), 1, 1);
+    int max_clusters = known_clusters;
+    if (max_clusters == 0 && cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0) {
+      std::lock_guard<std::mutex> lock(cache_mutex);
+      cache[dev].second = max_clusters;
+    }
+    if (max_clusters > 0 && max_clusters < pairs) cfg.gridDim = dim3((unsigned)(2 * max_clusters), 1, 1);
     return cudaLaunchKernelEx(&cfg, kern, mx, mu, (T *)y, (const T *)bias, g, sl, idesc);
   }
   const int grid = (int)std::min<long long>(p.n_items, sm_count);
