@@ -26,6 +26,7 @@ re-launches itself that way.
 """
 import argparse
 import json
+import math
 import os
 import socket
 import statistics
@@ -65,7 +66,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg2", "conv"])
+    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4", "conv"],
+                    help="vgg16 = BASELINE configs[4] (the headline); cfg1..cfg4 = the single-layer configs[0..3]; conv = --shape")
     ap.add_argument("--shape", default="256,256,56,3", help="--workload conv: C,K,HW,kernel (stride 1, 'same' padding, fp16)")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: 256 for vgg16, 32 for cfg2)")
     ap.add_argument("--algo", default="auto", choices=["auto", "row", "fused", "staged"],
@@ -345,14 +347,35 @@ def run_ours(args):
         metric = "vgg16_conv_images_per_s"
     else:
         from oracle import winograd_oracle as wo   # Kaiming-normal helper only; nothing timed runs in the oracle
-        batch = args.batch or 32
-        cc, kk, hw, ksz = (256, 256, 28, 3) if args.workload == "cfg2" else tuple(int(v) for v in args.shape.split(","))
-        w = wo.kaiming_normal((kk, cc, ksz, ksz), 1).half().to(dev)
+        # single-layer workloads: BASELINE configs[0..3] by name, or --shape
+        named = {
+            #        batch, C,   K,   spatial,        kernel,    stride, pad, dtype,         tile_m, input
+            "cfg1":  (8,   64,  64,  (56, 56),       (3, 3),    1,      1,   torch.float32, 2,      "normal"),
+            "cfg2":  (32,  256, 256, (28, 28),       (3, 3),    1,      1,   torch.float16, 4,      "normal"),
+            "cfg3a": (64,  3,   64,  (224, 224),     (7, 7),    2,      3,   torch.float16, 2,      "uniform"),
+            "cfg3b": (32,  128, 128, (56, 56),       (5, 5),    1,      2,   torch.float16, 2,      "normal"),
+            "cfg4":  (8,   64,  64,  (16, 56, 56),   (3, 3, 3), 1,      1,   torch.float16, 2,      "normal"),
+        }
+        if args.workload in named:
+            nb, cc, kk, sp, ks, stride, pad, dt, tm, dist_kind = named[args.workload]
+            batch = args.batch or nb
+        else:
+            cc, kk, hw_, ksz_ = tuple(int(v) for v in args.shape.split(","))
+            sp, ks, stride, pad, dt, tm, dist_kind = (hw_, hw_), (ksz_, ksz_), 1, ksz_ // 2, torch.float16, (4 if ksz_ == 3 else 2), "normal"
+            batch = args.batch or 32
+        hw = sp[-1]
+        ksz = ks[-1]
+        w = wo.kaiming_normal((kk, cc) + tuple(ks), 1).to(dt).to(dev)
         fused = args.algo in ("fused", "row")
-        algo_code = {"auto": capi.ALGO_STAGED, "row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
-        conv = engine.WinoConv((batch, hw, hw, cc), w, padding=ksz // 2, tile_m=2 if (fused or ksz != 3) else 4, algo=algo_code,
-                               product_dtype=torch.float16 if (args.product == "f16" and not fused) else None)
-        out_buf = torch.empty(conv.out_shape, dtype=torch.float16, device=dev)
+        # auto: the algorithm the config names (cfg2: staged F(4x4,3x3)); otherwise what the engine picks for 2-wide tiles
+        if args.algo == "auto":
+            algo_code = capi.ALGO_STAGED if (tm == 4 or dt == torch.float32) else capi.ALGO_AUTO
+        else:
+            algo_code = {"row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
+        conv = engine.WinoConv((batch,) + tuple(sp) + (cc,), w, stride=stride, padding=pad,
+                               tile_m=2 if (fused or tm == 2) else 4, algo=algo_code,
+                               product_dtype=torch.float16 if (args.product == "f16" and not fused and dt == torch.float16) else None)
+        out_buf = torch.empty(conv.out_shape, dtype=dt, device=dev)
 
         class _Single:
             layers = [conv]
@@ -370,14 +393,19 @@ def run_ours(args):
             acts = [out_buf]
 
         model = _Single()
-        x_host = torch.randn(batch, hw, hw, cc, generator=g).half().pin_memory()
+        x_host = (torch.rand if dist_kind == "uniform" else torch.randn)((batch,) + tuple(sp) + (cc,), generator=g).to(dt).pin_memory()
         layers = model.layers
-        workload = ("conv3x3_n32_c256_k256_28x28_f43 (BASELINE configs[1])" if args.workload == "cfg2"
-                    else f"conv{ksz}x{ksz}_n{batch}_c{cc}_k{kk}_{hw}x{hw}")
+        names = {"cfg1": "conv3x3_n8_c64_k64_56x56_fp32_f23 (BASELINE configs[0])",
+                 "cfg2": "conv3x3_n32_c256_k256_28x28_f43 (BASELINE configs[1])",
+                 "cfg3a": "conv7x7_s2_n64_c3_k64_224x224_dwm (BASELINE configs[2]a)",
+                 "cfg3b": "conv5x5_n32_c128_k128_56x56_dwm (BASELINE configs[2]b)",
+                 "cfg4": "conv3x3x3_n8_c64_k64_16x56x56 (BASELINE configs[3])"}
+        workload = names.get(args.workload, f"conv{ksz}x{ksz}_n{batch}_c{cc}_k{kk}_{hw}x{hw}")
         metric = "conv_images_per_s"
     x_dev = x_host.to(dev, non_blocking=True)
-    y_host = torch.empty(model.out_shape, dtype=torch.float16).pin_memory()
-    y_probe = torch.empty(model.out_shape, dtype=torch.float16, device=dev)
+    io_dtype = x_host.dtype
+    y_host = torch.empty(model.out_shape, dtype=io_dtype).pin_memory()
+    y_probe = torch.empty(model.out_shape, dtype=io_dtype, device=dev)
     torch.cuda.synchronize(dev)
 
     use_graph = not args.no_graph
@@ -479,7 +507,9 @@ def run_ours(args):
         st = [a / reps for a in acc]
         info = conv.info
         t_ms = sum(st)
-        t_tc = info.gemm_flops / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
+        # fp32 layers run their GEMM as fp32 FMA (a 10-bit tensor-core mantissa would not hold 1e-3): nominal 75 TFLOP/s
+        mma_peak = 75.0 if io_dtype == torch.float32 else peaks["bf16_tflops_sustained"]
+        t_tc = info.gemm_flops / (mma_peak * 1e12) * 1e3
         t_hbm = info.algorithmic_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
         per_layer.append({"layer": li + 1, "c": int(conv.desc.c_in), "k": int(conv.desc.k_out),
                           "hw": int(conv.in_shape[1]), "ms": round(t_ms, 4), "stage_ms": [round(v, 4) for v in st],
@@ -495,18 +525,21 @@ def run_ours(args):
     is_row = all(c.info.algo == capi.ALGO_ROW for c in layers)
     # fused paths: one dominant-kernel launch per layer (layer 1 adds a small channel-padding launch, timed with it)
     n_dom_launch = len(per_layer) if is_fused else sum(l["launches"] // 3 for l in per_layer)
-    esz = 2
+    esz = x_host.element_size()
     if dom == 1:
         alg = sum(c.info.gemm_flops for c in layers)
         achieved = alg / (stage_tot[1] * 1e-3) / 1e12
-        peak, unit, bound = peaks["bf16_tflops_sustained"], "TFLOP/s", "tensor"
-        kernel = "rowfused_kernel" if is_row else ("fused23_kernel" if is_fused else "gemm_tcgen05_kernel")
+        if io_dtype == torch.float32:
+            peak, unit, bound, kernel = 75.0, "TFLOP/s", "fp32-fma", "gemm_simt_kernel"
+        else:
+            peak, unit, bound = peaks["bf16_tflops_sustained"], "TFLOP/s", "tensor"
+            kernel = "rowfused_kernel" if is_row else ("fused23_kernel" if is_fused else "gemm_tcgen05_kernel")
     else:
         if dom == 0:   # algorithmic bytes of the input transform: it must read x once
-            alg = sum(float(esz) * c.desc.batch * c.in_shape[1] * c.in_shape[2] * c.desc.c_in for c in layers)
+            alg = sum(float(esz) * math.prod(c.in_shape) for c in layers)
             kernel = "input_transform_kernel"
         else:          # the output transform must write y once
-            alg = sum(float(esz) * c.out_shape[0] * c.out_shape[1] * c.out_shape[2] * c.out_shape[3] for c in layers)
+            alg = sum(float(esz) * math.prod(c.out_shape) for c in layers)
             kernel = "output_transform_kernel"
         achieved = alg / (stage_tot[dom] * 1e-3) / 1e9
         peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
@@ -525,7 +558,7 @@ def run_ours(args):
             cpu_baseline = {"value": round(v, 3), "unit": "images/s", "cores": cores, "kind": "port",
                             "sample": f"{n} images of the same stack in {el:.1f} s, fp32 F(2x2,3x3) tile algebra "
                                       "(reference torch-level path restated in oracle/)"}
-        else:
+        elif args.workload == "cfg2":
             v, n, el, cores = cpu_cfg2_layers_per_s(args.cpu_seconds)
             cpu_baseline = {"value": round(v * 32, 3), "unit": "images/s", "cores": cores, "kind": "port",
                             "sample": f"{n} passes of the same layer in {el:.1f} s, fp32 F(2x2,3x3), CPU"}
@@ -539,7 +572,7 @@ def run_ours(args):
     line = {
         "metric": metric, "value": round(value, 2), "unit": "images/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32" if io_dtype == torch.float32 else "f16", "data": "synthetic",
         "config": {"workload": workload, "per_gpu_batch": batch, "global_batch": int(total_images),
                    "parallelism": f"batch shards x{world}, no collective", "launch": "cuda_graph" if use_graph else "eager",
                    "l2": "activations and scratch of every step exceed the 126 MB L2 (inputs larger than L2)",

@@ -175,13 +175,29 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
   plan->row = false;
   if (fused_ok && (d->algo == WINOCONV_ALGO_AUTO || d->algo == WINOCONV_ALGO_ROW)) {
     RowDesc &r = plan->rd;
-    r.N = g.N; r.C = g.C; r.K = g.K; r.D = g.D; r.H = g.H; r.W = g.W; r.oD = g.oD; r.oH = g.oH; r.oW = g.oW;
-    r.yH = g.yH; r.yW = g.yW; r.sD = g.sD; r.sH = g.sH; r.sW = g.sW; r.pD = g.pD; r.pH = g.pH; r.pW = g.pW;
-    r.kD = g.kD; r.kH = g.kH; r.kW = g.kW; r.epilogue = g.epilogue; r.weight_layout = g.weight_layout;
-    plan->row = rowfused_plan(r, &plan->rp);
+    std::memset(&r, 0, sizeof(r));
+    r.N = g.N; r.K = g.K; r.oD = g.oD; r.oH = g.oH; r.oW = g.oW; r.yH = g.yH; r.yW = g.yW;
+    r.epilogue = g.epilogue; r.weight_layout = g.weight_layout;
+    r.C0 = g.C; r.D0 = g.D; r.H0 = g.H; r.W0 = g.W; r.pD0 = g.pD; r.pH0 = g.pH; r.pW0 = g.pW;
+    r.kD0 = g.kD; r.kH0 = g.kH; r.kW0 = g.kW;
+    const bool strides_ok = (g.sD == 1 || g.sD == 2) && (g.sH == 1 || g.sH == 2) && (g.sW == 1 || g.sW == 2);
+    r.fD = g.sD; r.fH = g.sH; r.fW = g.sW;
+    r.phases = strides_ok ? g.sD * g.sH * g.sW : 0;
+    if (r.phases == 1) {
+      r.C = g.C; r.D = g.D; r.H = g.H; r.W = g.W; r.pD = g.pD; r.pH = g.pH; r.pW = g.pW; r.kD = g.kD; r.kH = g.kH; r.kW = g.kW;
+    } else if (r.phases > 1) {
+      // stride 2: y[o] = sum_t x[2 o + t] w[t] with t = 2 a + phase is a stride-1 convolution over the two
+      // polyphase parts of x taken as extra channels, kernel ceil(k / 2), input extent out + k' - 1, no padding
+      r.C = r.phases * g.C;
+      r.kD = (g.kD + g.sD - 1) / g.sD; r.kH = (g.kH + g.sH - 1) / g.sH; r.kW = (g.kW + g.sW - 1) / g.sW;
+      r.D = g.oD + r.kD - 1; r.H = g.oH + r.kH - 1; r.W = g.oW + r.kW - 1;
+      r.pD = r.pH = r.pW = 0;
+    }
+    r.sD = r.sH = r.sW = 1;
+    plan->row = r.phases >= 1 && rowfused_plan(r, &plan->rp);
   }
   if (d->algo == WINOCONV_ALGO_ROW && !plan->row)
-    return fail(WINOCONV_ERR_UNSUPPORTED, "the row-piece kernel needs f16 / bf16, tile_m = 2, stride 1, a kernel at most 7 taps tall, the tcgen05 engine and fp32 products");
+    return fail(WINOCONV_ERR_UNSUPPORTED, "the row-piece kernel needs f16 / bf16, tile_m = 2, strides of 1 or 2, a kernel at most 7 taps tall (14 at stride 2), the tcgen05 engine and fp32 products");
   if (d->algo == WINOCONV_ALGO_FUSED && !fused_ok)
     return fail(WINOCONV_ERR_UNSUPPORTED, "the fused path needs f16 / bf16, tile_m = 2 (or 0 with a kernel other than 2-D 3x3 stride 1), the tcgen05 engine and fp32 products");
   plan->fused = fused_ok && !plan->row && d->algo != WINOCONV_ALGO_STAGED && d->algo != WINOCONV_ALGO_ROW;
@@ -245,17 +261,20 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
     I.algo = WINOCONV_ALGO_ROW;
     I.tile_m[0] = 1; I.tile_m[1] = 1; I.tile_m[2] = 2;
     I.tiles_per_dim[0] = g.oD; I.tiles_per_dim[1] = g.oH; I.tiles_per_dim[2] = (g.oW + 1) / 2;
-    I.n_pieces = g.kD * g.kH * rp.PW; I.positions = 4;
+    I.n_pieces = plan->rd.kD * plan->rd.kH * rp.PW; I.positions = 4;
     I.tiles = (long long)g.N * g.oD * g.oH * ((g.oW + 1) / 2);
     I.filter_bytes = (unsigned long long)rp.filter_elems * esz;
-    // scratch only to zero-pad the channels of x to a multiple of 8 (TMA needs 16-byte pixel strides)
-    I.input_ws_bytes = I.input_ws_bytes_min = (rp.Cp != g.C) ? (unsigned long long)g.N * g.D * g.H * g.W * rp.Cp * esz : 0ull;
+    // scratch only to zero-pad the channels of x to a multiple of 8 (TMA needs 16-byte pixel strides), or to hold
+    // the input with its stride-2 phases gathered into channels
+    const RowDesc &rd = plan->rd;
+    I.input_ws_bytes = I.input_ws_bytes_min =
+        (rd.phases > 1 || rp.Cp != g.C) ? (unsigned long long)rd.N * rd.D * rd.H * rd.W * rp.Cp * esz : 0ull;
     I.product_ws_bytes = I.product_ws_bytes_min = 0;
     I.block_tiles = I.tiles;
   }
   I.direct_flops = 2.0 * g.N * g.K * g.C * (double)ks[0] * ks[1] * ks[2] * (double)out[0] * out[1] * out[2];
   I.gemm_flops = plan->fused ? 2.0 * 16 * (double)plan->fg.T * plan->fg.P * g.C * g.K : 2.0 * pos * (double)g.T * g.C * g.K;
-  if (plan->row) I.gemm_flops = 2.0 * 4 * (double)I.tiles * I.n_pieces * g.C * g.K;
+  if (plan->row) I.gemm_flops = 2.0 * 4 * (double)I.tiles * I.n_pieces * plan->rd.C * g.K;
   I.algorithmic_bytes = (double)esz * ((double)g.N * g.D * g.H * g.W * g.C + (double)g.K * g.C * ks[0] * ks[1] * ks[2] +
                                        (double)g.N * g.yD * g.yH * g.yW * g.K);
   return WINOCONV_OK;

@@ -37,6 +37,14 @@ struct RowDesc {
   int sD, sH, sW, pD, pH, pW, kD, kH, kW;
   unsigned epilogue;
   int weight_layout;
+  // Stride 2 as a stride-1 problem (polyphase parts folded into the channels): when `phases` > 1 the fields above
+  // describe the stride-1 convolution the kernel runs -- C = phases x C0 channels, kernel ceil(k0 / 2) per strided
+  // dimension, no padding, input extent out + k - 1 -- and the fields below the tensor the caller passes in.
+  int phases;                 // 1: plain stride-1 problem
+  int fD, fH, fW;             // phase count per dimension (1 or 2)
+  int C0, D0, H0, W0;         // caller's input [N, D0, H0, W0, C0]
+  int pD0, pH0, pW0;          // caller's padding
+  int kD0, kH0, kW0;          // caller's kernel
 };
 struct RowPlan {
   int Cp, PW, BN, MB, CBW, RB, n_rb, n_cb, slab_rows, patch_h, patch_w, n_chunks, n_nblocks, slabs;

@@ -794,9 +794,15 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 }
 
 // U[slab][k][c], slab = ((kd * kH + kh) * PW + w) * 4 + j:  G (3 taps of window w, zero padded) along W.
+// With phases (stride 2 folded into channels) channel c = phase * C0 + c0 and tap (kd, kh, kw) of the stride-1 kernel is
+// tap (fD * kd + phase_d, fH * kh + phase_h, fW * kw + phase_w) of the caller's kernel (zero beyond its extent).
+struct FilterPhases {
+  int on, fD, fH, fW, C0, kD0, kH0, kW0;
+};
 template <typename T>
 __global__ void __launch_bounds__(256) rowfused_filter_kernel(const T *__restrict__ wgt, T *__restrict__ u, int C, int Cp,
-                                                              int K, int kD, int kH, int kW, int PW, int layout) {
+                                                              int K, int kD, int kH, int kW, int PW, int layout,
+                                                              FilterPhases ph) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long per_k = (long long)kD * kH * PW * Cp;
   if (idx >= per_k * K) return;
@@ -808,12 +814,24 @@ __global__ void __launch_bounds__(256) rowfused_filter_kernel(const T *__restric
   const int kd = (int)(rem / kH);
   float a[3] = {0.f, 0.f, 0.f}, o[4];
   if (c < C) {
+    // the caller's channel and kernel extents, and this element's phase offsets
+    int c0 = c, C0 = C, eD = kD, eH = kH, eW = kW, fD = 1, fH = 1, fW = 1, pd = 0, phh = 0, pw = 0;
+    if (ph.on) {
+      C0 = ph.C0; eD = ph.kD0; eH = ph.kH0; eW = ph.kW0; fD = ph.fD; fH = ph.fH; fW = ph.fW;
+      int phase = c / C0;
+      c0 = c - phase * C0;
+      pw = phase % fW; phase /= fW;
+      phh = phase % fH; phase /= fH;
+      pd = phase;
+    }
+    const int td = fD * kd + pd, th = fH * kh + phh;
 #pragma unroll
     for (int t = 0; t < 3; ++t) {
       const int kw = 3 * w + t;
-      if (kw < kW) {
-        const long long off = layout == WINOCONV_W_KCRS ? ((((long long)k * C + c) * kD + kd) * kH + kh) * kW + kw
-                                                        : ((((long long)kd * kH + kh) * kW + kw) * C + c) * K + k;
+      const int tw = fW * kw + pw;
+      if (kw < kW && td < eD && th < eH && tw < eW) {
+        const long long off = layout == WINOCONV_W_KCRS ? ((((long long)k * C0 + c0) * eD + td) * eH + th) * eW + tw
+                                                        : ((((long long)td * eH + th) * eW + tw) * C0 + c0) * K + k;
         a[t] = Elem<T>::load(wgt + off);
       }
     }
@@ -838,6 +856,45 @@ __global__ void __launch_bounds__(256) pad_channels_kernel(const T *__restrict__
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = (c0 + i < C) ? x[px * C + c0 + i] : T(0.f);
   *reinterpret_cast<uint4 *>(xp + px * Cp + c0) = *reinterpret_cast<const uint4 *>(v);
+}
+
+// Stride 2 -> stride 1: xs[n][id][ih][iw][phase * C0 + c] = x_padded[n][fD * id + pd][fH * ih + ph][fW * iw + pw][c]
+// (zero outside the caller's tensor and in the channels that pad phases * C0 to a multiple of 8).  One thread writes
+// one 16-byte group of eight channels.
+struct PhaseGeom {
+  int N, D, H, W, Cp;          // destination extents (stride-1 problem)
+  int fD, fH, fW, C0, D0, H0, W0, pD0, pH0, pW0;
+};
+template <typename T>
+__global__ void __launch_bounds__(256) phases_to_channels_kernel(const T *__restrict__ x, T *__restrict__ xs, PhaseGeom q) {
+  const int groups = q.Cp / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long pixels = (long long)q.N * q.D * q.H * q.W;
+  if (idx >= pixels * groups) return;
+  long long px = idx / groups;
+  const int cg = (int)(idx - px * groups) * 8;
+  const int iw = (int)(px % q.W); px /= q.W;
+  const int ih = (int)(px % q.H); px /= q.H;
+  const int id = (int)(px % q.D);
+  const int n = (int)(px / q.D);
+  const int C = q.fD * q.fH * q.fW * q.C0;
+  __align__(16) T v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = cg + i;
+    T val = T(0.f);
+    if (c < C) {
+      int phase = c / q.C0;
+      const int c0 = c - phase * q.C0;
+      const int pw = phase % q.fW; phase /= q.fW;
+      const int ph = phase % q.fH; phase /= q.fH;
+      const int sd = q.fD * id + phase - q.pD0, sh = q.fH * ih + ph - q.pH0, sw = q.fW * iw + pw - q.pW0;
+      if (sd >= 0 && sd < q.D0 && sh >= 0 && sh < q.H0 && sw >= 0 && sw < q.W0)
+        val = x[((((long long)n * q.D0 + sd) * q.H0 + sh) * q.W0 + sw) * q.C0 + c0];
+    }
+    v[i] = val;
+  }
+  *reinterpret_cast<uint4 *>(xs + idx * 8) = *reinterpret_cast<const uint4 *>(v);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -936,10 +993,14 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
 cudaError_t launch_rowfused_filter_transform(const RowDesc &d, const RowPlan &p, int dtype, const void *w, void *u, cudaStream_t s) {
   const long long n = (long long)d.kD * d.kH * p.PW * p.Cp * d.K;
   const unsigned blocks = (unsigned)((n + 255) / 256);
+  rowf::FilterPhases ph = {};
+  if (d.phases > 1) {
+    ph.on = 1; ph.fD = d.fD; ph.fH = d.fH; ph.fW = d.fW; ph.C0 = d.C0; ph.kD0 = d.kD0; ph.kH0 = d.kH0; ph.kW0 = d.kW0;
+  }
   if (dtype == WINOCONV_F16)
-    rowf::rowfused_filter_kernel<__half><<<blocks, 256, 0, s>>>((const __half *)w, (__half *)u, d.C, p.Cp, d.K, d.kD, d.kH, d.kW, p.PW, d.weight_layout);
+    rowf::rowfused_filter_kernel<__half><<<blocks, 256, 0, s>>>((const __half *)w, (__half *)u, d.C, p.Cp, d.K, d.kD, d.kH, d.kW, p.PW, d.weight_layout, ph);
   else
-    rowf::rowfused_filter_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16 *)w, (__nv_bfloat16 *)u, d.C, p.Cp, d.K, d.kD, d.kH, d.kW, p.PW, d.weight_layout);
+    rowf::rowfused_filter_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16 *)w, (__nv_bfloat16 *)u, d.C, p.Cp, d.K, d.kD, d.kH, d.kW, p.PW, d.weight_layout, ph);
   return cudaGetLastError();
 }
 
@@ -1024,7 +1085,22 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { *detail = "cuTensorMapEncodeTiled unavailable"; return cudaErrorNotSupported; }
   const void *xin = x;
-  if (p.Cp != d.C) {   // channels not a multiple of 8: TMA needs 16-byte pixel strides, so pad into scratch first
+  if (d.phases > 1) {   // stride 2: gather the polyphase parts into channels (and pad them to a multiple of 8)
+    if (!pad_ws) { *detail = "phase-gather scratch missing"; return cudaErrorInvalidValue; }
+    PhaseGeom q;
+    q.N = d.N; q.D = d.D; q.H = d.H; q.W = d.W; q.Cp = p.Cp;
+    q.fD = d.fD; q.fH = d.fH; q.fW = d.fW; q.C0 = d.C0; q.D0 = d.D0; q.H0 = d.H0; q.W0 = d.W0;
+    q.pD0 = d.pD0; q.pH0 = d.pH0; q.pW0 = d.pW0;
+    const long long groups = (long long)d.N * d.D * d.H * d.W * (p.Cp / 8);
+    const unsigned blocks = (unsigned)((groups + 255) / 256);
+    if (dtype == WINOCONV_F16)
+      phases_to_channels_kernel<__half><<<blocks, 256, 0, s>>>((const __half *)x, (__half *)pad_ws, q);
+    else
+      phases_to_channels_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)pad_ws, q);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { *detail = "phase gather launch failed"; return e; }
+    xin = pad_ws;
+  } else if (p.Cp != d.C) {   // channels not a multiple of 8: TMA needs 16-byte pixel strides, so pad into scratch first
     if (!pad_ws) { *detail = "channel padding scratch missing"; return cudaErrorInvalidValue; }
     const long long pixels = (long long)d.N * d.D * d.H * d.W;
     const unsigned blocks = (unsigned)((pixels * (p.Cp / 8) + 255) / 256);

@@ -82,10 +82,15 @@ def test_row_piece_plan():
     rgb = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=3, k_out=64, in_size=(224, 224), ker_size=3, pad=1, tile_m=2))
     assert rgb.algo == capi.ALGO_ROW and rgb.c_pad == 8 and rgb.input_ws_bytes == 4 * 224 * 224 * 8 * 2
     s2 = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=16, k_out=64, in_size=(64, 64), ker_size=7, stride=2, pad=3))
-    assert s2.algo == capi.ALGO_FUSED                       # stride 2 falls to the 3x3-piece kernel
-    with pytest.raises(capi.WinoconvError) as ei:
-        capi.plan(capi.make_desc(ndim=2, batch=4, c_in=16, k_out=64, in_size=(64, 64), ker_size=7, stride=2, pad=3, algo=capi.ALGO_ROW))
-    assert ei.value.status == capi.ERR_UNSUPPORTED
+    # stride 2 runs on the row kernel as a stride-1 problem: 4 phases x 16 channels, 4 x 4 kernel (4 rows x 2 windows),
+    # input gathered into scratch as [4, 32 + 3, 32 + 3, 64]
+    assert s2.algo == capi.ALGO_ROW and s2.n_pieces == 8 and s2.input_ws_bytes == 4 * 35 * 35 * 64 * 2
+    assert s2.gemm_flops == pytest.approx(2.0 * 4 * s2.tiles * 8 * 64 * 64)
+    s2f = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=16, k_out=64, in_size=(64, 64), ker_size=7, stride=2, pad=3, algo=capi.ALGO_FUSED))
+    assert s2f.algo == capi.ALGO_FUSED                      # the 3x3-piece kernel on request
+    with pytest.raises(capi.WinoconvError) as ei:           # stride 3 is no Winograd / DWM case of either single-kernel path
+        capi.plan(capi.make_desc(ndim=2, batch=4, c_in=16, k_out=64, in_size=(64, 64), ker_size=7, stride=3, pad=3, algo=capi.ALGO_ROW))
+    assert ei.value.status in (capi.ERR_UNSUPPORTED, capi.ERR_INVALID_ARGUMENT)
 
 
 def test_fused_refused_where_it_does_not_apply():

@@ -71,7 +71,7 @@ def test_fused_cases(n, c, k, sp, ks, stride, pad, m, dtype):
     check_against_oracle(x, w, y, stride=stride, padding=pad)
 
 
-ROW_CASES = [c for c in SMALL + FUSED_EXTRA if c[5] == 1 and c[7] != 4 and c[4][-2] <= 7] + [
+ROW_CASES = [c for c in SMALL + FUSED_EXTRA if c[7] != 4 and c[4][-2] <= 7 * c[5]] + [
     (2, 32, 64, (16, 64), (3, 3), 1, 1, 2),        # exactly one 8 x 16 block per image, one channel slab
     (1, 64, 128, (40, 70), (3, 3), 1, 1, 2),       # N = 128 accumulators, ragged blocks in both directions
     (2, 96, 192, (14, 14), (3, 3), 1, 1, 2),       # 16 x 8 block shape, two channel blocks, slab tail
@@ -81,6 +81,10 @@ ROW_CASES = [c for c in SMALL + FUSED_EXTRA if c[5] == 1 and c[7] != 4 and c[4][
     (5, 24, 64, (17, 23), (3, 3), 1, 1, 2),        # CTA pairs at 64-wide accumulators (two TMEM buffers), odd batch
     (4, 256, 256, (28, 28), (3, 3), 1, 1, 2),      # eight channel slabs, filter slabs streamed through the ring
     (2, 512, 128, (14, 14), (3, 3), 1, 1, 2),      # sixteen channel slabs, one channel block
+    (3, 3, 64, (61, 57), (7, 7), 2, 3, 2),         # stride 2: four polyphase parts as 12 channels, 4 x 4 stride-1 kernel
+    (2, 40, 72, (23, 30), (3, 3), 2, 1, 2),        # stride 2, 3 x 3: parts of 2 x 2, 2 x 1, 1 x 2, 1 x 1 taps
+    (1, 16, 32, (20, 21), (5, 5), 2, 0, 2),        # stride 2 without padding, odd extents
+    (1, 8, 16, (9, 12, 11), (3, 3, 3), 2, 1, 2),   # 3-D stride 2: eight phases
 ]
 
 
@@ -203,12 +207,15 @@ def test_cfg2_fp16_f43(product_dtype):
 ALGOS = [(capi.ALGO_STAGED, "staged"), (capi.ALGO_FUSED, "fused"), (capi.ALGO_ROW, "row")]
 
 
-@pytest.mark.parametrize("algo,name", ALGOS[:2])      # stride 2: the row-piece kernel does not apply
+@pytest.mark.parametrize("algo,name", ALGOS)
 def test_cfg3a_fp16_7x7_stride2(algo, name):
     x = seeded((64, 3, 224, 224), 0, dist="uniform", dtype=torch.float16)
     w = wo.kaiming_normal((64, 3, 7, 7), 1).half()
     y, conv = run_engine(x, w, stride=2, padding=3, algo=algo)
-    assert (conv.info.n_pieces, conv.info.positions) == ((9, 100) if algo == capi.ALGO_STAGED else (9, 16))
+    # staged: 9 polyphase / DWM pieces, 100 positions; 3x3-piece kernel: the same 9 pieces at 16 positions;
+    # row kernel: 4 phases as channels, a 4 x 4 stride-1 kernel = 4 rows x 2 windows of 4 positions
+    expect = {capi.ALGO_STAGED: (9, 100), capi.ALGO_FUSED: (9, 16), capi.ALGO_ROW: (8, 4)}[algo]
+    assert (conv.info.n_pieces, conv.info.positions) == expect
     print("cfg3a engine", name, check_against_oracle(x, w, y, stride=2, padding=3))
 
 
@@ -235,7 +242,8 @@ def test_auto_resolves_to_fused_for_16bit_f2_and_staged_otherwise():
     w5 = wo.kaiming_normal((8, 8, 5, 5), 2).half()
     w3 = wo.kaiming_normal((8, 8, 3, 3), 3).half()
     assert run_engine(x, w5, padding=2)[1].info.algo == capi.ALGO_ROW
-    assert run_engine(x, w5, padding=2, stride=2)[1].info.algo == capi.ALGO_FUSED   # stride 2: 3x3 pieces
+    assert run_engine(x, w5, padding=2, stride=2)[1].info.algo == capi.ALGO_ROW     # stride 2: phases folded into channels
+    assert run_engine(x, w5, padding=2, stride=2, algo=capi.ALGO_FUSED)[1].info.algo == capi.ALGO_FUSED
     assert run_engine(x, w3, padding=1)[1].info.algo == capi.ALGO_ROW             # 16-bit: 2-wide tiles, one kernel
     assert run_engine(x, w3, padding=1, tile_m=2)[1].info.algo == capi.ALGO_ROW
     c4 = run_engine(x, w3, padding=1, tile_m=4)[1]                                # F(4x4,3x3) on request: staged
