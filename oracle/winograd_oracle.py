@@ -260,6 +260,89 @@ def winograd_conv_cpu(x: torch.Tensor, w: torch.Tensor, stride=1, padding=0, til
 
 
 # --------------------------------------------------------------------------------------
+# the two rearrangements the engine's single-kernel path makes (restated to pin their algebra)
+# --------------------------------------------------------------------------------------
+def phases_to_channels_cpu(x: torch.Tensor, w: torch.Tensor, stride, padding):
+    """A stride-{1,2} convolution as a stride-1, unpadded one: y[o] = sum_t xpad[s o + t] w[t] with
+    t = s a + phase becomes, per strided dimension, a sum over `phase` (carried as extra channels,
+    channel = phase_index * C + c, phases ordered depth-major) and over a < ceil(k / s).
+    The reference scaffolds this polyphase scheme (``src/winograd_conv.cpp:45-51,61-68`` and the 4x4,
+    4x3, 3x4 parts of ``base_conv_launchers.h:68-94``) without finishing it.
+    x [N,C,*sp], w [K,C,*k] -> (xs [N, P*C, *(out + k' - 1)], ws [K, P*C, *k'])."""
+    nd = x.dim() - 2
+    stride = [stride] * nd if isinstance(stride, int) else list(stride)
+    padding = [padding] * nd if isinstance(padding, int) else list(padding)
+    x = x.detach().cpu().double()
+    w = w.detach().cpu().double()
+    n, c = x.shape[:2]
+    k_out = w.shape[0]
+    ks = list(w.shape[2:])
+    outs = [(x.shape[2 + i] + 2 * padding[i] - ks[i]) // stride[i] + 1 for i in range(nd)]
+    k2 = [-(-ks[i] // stride[i]) for i in range(nd)]
+    ext = [outs[i] + k2[i] - 1 for i in range(nd)]
+    # pad on the left by `padding`, on the right up to the last element any phase touches
+    padspec = []
+    for i in reversed(range(nd)):
+        right = stride[i] * ext[i] - padding[i] - x.shape[2 + i]
+        padspec += [padding[i], max(right, 0)]
+    xp = F.pad(x, padspec)
+    phases = list(itertools.product(*[range(s) for s in stride]))
+    xs = torch.zeros((n, len(phases) * c, *ext), dtype=torch.float64)
+    ws = torch.zeros((k_out, len(phases) * c, *k2), dtype=torch.float64)
+    for pi, ph in enumerate(phases):
+        xi = (slice(None), slice(None)) + tuple(slice(ph[i], ph[i] + stride[i] * ext[i], stride[i]) for i in range(nd))
+        xs[:, pi * c:(pi + 1) * c] = xp[xi]
+        wi = (slice(None), slice(None)) + tuple(slice(ph[i], None, stride[i]) for i in range(nd))
+        part = w[wi]
+        dst = (slice(None), slice(pi * c, (pi + 1) * c)) + tuple(slice(0, part.shape[2 + i]) for i in range(nd))
+        ws[dst] = part
+    return xs, ws
+
+
+def row_piece_conv_cpu(x: torch.Tensor, w: torch.Tensor, padding=0, dtype=torch.float64) -> torch.Tensor:
+    """Stride-1 convolution by 1 x 3 DWM pieces, the decomposition of the engine's row kernel: along the last
+    dimension every run of three taps is an F(2,3) window (zero taps where the kernel ends; the piece rule
+    of ``src/base_conv_launchers.h:58-388`` cuts at multiples of 3 too), along every other dimension each
+    tap is its own piece, for which F(m,1) is the identity.  All pieces share the four Winograd positions
+    of a 1 x 2 output tile, so they are summed before the output transform:
+        M[j] = sum_{taps, window} (B^T d)[j] * (G g)[j],   y = A^T M
+    with the F(2,3) matrices of ``matrix_conv.py:12-29`` (B^T rows (1,0,-1,0), (0,1,1,0), (0,-1,1,0), (0,1,0,-1);
+    G rows (1,0,0), (.5,.5,.5), (.5,-.5,.5), (0,0,1); A^T rows (1,1,1,0), (0,1,-1,-1))."""
+    nd = x.dim() - 2
+    padding = [padding] * nd if isinstance(padding, int) else list(padding)
+    x = x.detach().cpu().to(dtype)
+    w = w.detach().cpu().to(dtype)
+    padspec = []
+    for p in reversed(padding):
+        padspec += [p, p]
+    xp = F.pad(x, padspec)
+    ks = list(w.shape[2:])
+    outs = [xp.shape[2 + i] - ks[i] + 1 for i in range(nd)]
+    n_pairs = -(-outs[-1] // 2)
+    n_win = -(-ks[-1] // 3)
+    bt = torch.tensor([[1, 0, -1, 0], [0, 1, 1, 0], [0, -1, 1, 0], [0, 1, 0, -1]], dtype=dtype)
+    g = torch.tensor([[1, 0, 0], [.5, .5, .5], [.5, -.5, .5], [0, 0, 1]], dtype=dtype)
+    at = torch.tensor([[1, 1, 1, 0], [0, 1, -1, -1]], dtype=dtype)
+    # zero-extend the last dimension so every window of every column pair is inside the tensor
+    need_w = 2 * n_pairs + 3 * n_win - 1
+    xp = F.pad(xp, [0, max(need_w - xp.shape[-1], 0)])
+    m = torch.zeros((x.shape[0], w.shape[0], *outs[:-1], n_pairs, 4), dtype=dtype)
+    for taps in itertools.product(*[range(k) for k in ks[:-1]]):
+        for win in range(n_win):
+            gw = torch.zeros((w.shape[0], w.shape[1], 3), dtype=dtype)
+            hi = min(3 * win + 3, ks[-1])
+            gw[..., :hi - 3 * win] = w[(slice(None), slice(None)) + taps + (slice(3 * win, hi),)]
+            u = torch.einsum("jt,kct->kcj", g, gw)                                   # [K, C, 4]
+            xi = (slice(None), slice(None)) + tuple(slice(t, t + o) for t, o in zip(taps, outs[:-1]))
+            rows = xp[xi]                                                            # [N, C, *outs[:-1], W]
+            d = torch.stack([rows[..., 2 * q + 3 * win: 2 * q + 3 * win + 4] for q in range(n_pairs)], dim=-2)
+            v = torch.einsum("ji,...qi->...qj", bt, d)                               # [N, C, ..., pairs, 4]
+            m += torch.einsum("nc...qj,kcj->nk...qj", v, u)
+    y = torch.einsum("oj,...qj->...qo", at, m).reshape(*m.shape[:-2], 2 * n_pairs)
+    return y[..., :outs[-1]]
+
+
+# --------------------------------------------------------------------------------------
 # workload descriptions shared by tests and the bench
 # --------------------------------------------------------------------------------------
 VGG16_CHANNELS = [(3, 64), (64, 64), (64, 128), (128, 128), (128, 256), (256, 256), (256, 256),

@@ -101,3 +101,44 @@ def test_fp16_emulation_error_is_reported_not_zero():
     e32 = wo.error_metrics(wo.winograd_conv_cpu(x, w, padding=1), o)["E_B"]
     e16 = wo.error_metrics(wo.winograd_conv_cpu(x, w, padding=1, fp16=True), o)["E_B"]
     assert e32 < 1e-5 < e16 < 5e-2
+
+
+@pytest.mark.parametrize("n,c,k,sp,ks,pad", [
+    (2, 3, 4, (9, 10), (3, 3), 1),
+    (1, 5, 2, (8, 11), (5, 5), 2),        # two windows along W, the second with two taps
+    (1, 2, 3, (7, 9), (7, 7), 3),         # three windows, the last with one tap
+    (1, 3, 2, (6, 7), (1, 3), 0),
+    (1, 2, 2, (5, 6, 7), (3, 3, 3), 1),   # 3-D: depth and row taps are identity pieces
+    (1, 2, 2, (9, 9), (4, 4), 0),
+])
+def test_row_piece_decomposition_equals_direct(n, c, k, sp, ks, pad):
+    """1 x 3 DWM pieces (F(2,3) along W, identity pieces along the other dimensions) summed in the Winograd
+    domain give the direct convolution: the algebra of the engine's row kernel."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(n, c, *sp, generator=g, dtype=torch.float64)
+    w = torch.randn(k, c, *ks, generator=g, dtype=torch.float64)
+    y = wo.row_piece_conv_cpu(x, w, padding=pad)
+    o = wo.direct_conv_f64(x, w, padding=pad)
+    assert y.shape == o.shape
+    assert (y - o).abs().max().item() < 1e-11
+
+
+@pytest.mark.parametrize("n,c,k,sp,ks,stride,pad", [
+    (2, 3, 4, (15, 14), (7, 7), 2, 3),             # the 7x7 stride-2 case: 4x4, 4x3, 3x4, 3x3 parts
+    (1, 2, 3, (9, 10), (3, 3), 2, 1),
+    (1, 4, 2, (11, 8), (5, 5), 2, 0),              # odd extents, no padding
+    (1, 2, 2, (7, 8, 9), (3, 3, 3), 2, 1),         # 3-D: eight phases
+    (1, 2, 2, (9, 12), (3, 5), (1, 2), (1, 2)),    # stride 2 along W only
+])
+def test_stride2_as_stride1_over_phase_channels(n, c, k, sp, ks, stride, pad):
+    """Folding the polyphase parts of a stride-2 convolution into channels leaves a stride-1, unpadded
+    convolution with the same result (how the engine runs stride 2 on its stride-1 kernel)."""
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(n, c, *sp, generator=g, dtype=torch.float64)
+    w = torch.randn(k, c, *ks, generator=g, dtype=torch.float64)
+    xs, ws = wo.phases_to_channels_cpu(x, w, stride, pad)
+    o = wo.direct_conv_f64(x, w, stride=stride, padding=pad)
+    y = wo.direct_conv_f64(xs, ws)
+    assert y.shape == o.shape and (y - o).abs().max().item() < 1e-11
+    # and through the row-piece decomposition, as the device does
+    assert (wo.row_piece_conv_cpu(xs, ws) - o).abs().max().item() < 1e-10
