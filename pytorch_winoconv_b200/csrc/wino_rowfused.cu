@@ -453,7 +453,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   } else if (warp < B_WARP) {
     // ---------------------------------------------------------------- F(2,3) along W: raw patch -> four slabs
     const int ptid = threadIdx.x - 32;                 // 0..N_PROD-1
-    const int v = ptid & 3;                            // 16-byte vector of the 32-channel slab
     const int n_tasks = g.slab_rows;                   // one task = one slab row (input row, column pair) x one vector
     uint32_t it_raw = 0, it_a = 0;
     int as = 0;
@@ -470,6 +469,14 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         if (ok == 0u) { alive = false; break; }
         if (ptid == 0) TL(8, it_raw);
         const uint8_t *raw = base_ptr + sl.off_raw[rs];
+        // A slab with at most 16 real channels (few-channel input, phase-gathered RGB, the tail of C) is read by the
+        // MMAs through one K = 16 step, i.e. the first two 16-byte vectors of each row: only those are produced, and
+        // a vector past the last real channel is written as zeros without touching the patch.
+        const int ch0 = (step % g.n_chunks) * KC;
+        const bool narrow = g.Cp - ch0 <= UMMA_K;
+        const int vshift = narrow ? 1 : 2;
+        const int v = ptid & ((1 << vshift) - 1);           // 16-byte vector of the 32-channel slab
+        const bool real = ch0 + v * 8 < g.Cp;
         for (int w = 0; w < g.PW && alive; ++w) {
           ok = 0;
           if (lane == 0) ok = mbar_wait(a_empty(as), a_par, abort_word, ERR_PROD_A) ? 1u : 0u;
@@ -478,15 +485,22 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           if (ptid == 0) TL(4, it_a);
           uint8_t *slab = base_ptr + sl.off_a[as];
           const int slab_bytes = g.slab_rows * 64;
-          for (int row = ptid >> 2; row < (ROW_DBG(g, 4u) ? 0 : n_tasks); row += N_PROD / 4) {
+          for (int row = ptid >> vshift; row < (ROW_DBG(g, 4u) ? 0 : n_tasks); row += N_PROD >> vshift) {
             const int ir = row >> cbw_shift, cp = row - (ir << cbw_shift);
-            const uint8_t *src = raw + ((size_t)(ir * g.patch_w + 2 * cp + 3 * w) * KC + v * 8) * 2;
-            V8<T> d0, d1, d2, d3;
-            *reinterpret_cast<uint4 *>(&d0) = *reinterpret_cast<const uint4 *>(src);
-            *reinterpret_cast<uint4 *>(&d1) = *reinterpret_cast<const uint4 *>(src + KC * 2);
-            *reinterpret_cast<uint4 *>(&d2) = *reinterpret_cast<const uint4 *>(src + 2 * KC * 2);
-            *reinterpret_cast<uint4 *>(&d3) = *reinterpret_cast<const uint4 *>(src + 3 * KC * 2);
-            const V8<T> o0 = v8_sub<T>(d0, d2), o1 = v8_add<T>(d1, d2), o2 = v8_sub<T>(d2, d1), o3 = v8_sub<T>(d1, d3);
+            V8<T> o0, o1, o2, o3;
+            if (real) {
+              const uint8_t *src = raw + ((size_t)(ir * g.patch_w + 2 * cp + 3 * w) * KC + v * 8) * 2;
+              V8<T> d0, d1, d2, d3;
+              *reinterpret_cast<uint4 *>(&d0) = *reinterpret_cast<const uint4 *>(src);
+              *reinterpret_cast<uint4 *>(&d1) = *reinterpret_cast<const uint4 *>(src + KC * 2);
+              *reinterpret_cast<uint4 *>(&d2) = *reinterpret_cast<const uint4 *>(src + 2 * KC * 2);
+              *reinterpret_cast<uint4 *>(&d3) = *reinterpret_cast<const uint4 *>(src + 3 * KC * 2);
+              o0 = v8_sub<T>(d0, d2); o1 = v8_add<T>(d1, d2); o2 = v8_sub<T>(d2, d1); o3 = v8_sub<T>(d1, d3);
+            } else {
+              const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+              *reinterpret_cast<uint4 *>(&o0) = z; *reinterpret_cast<uint4 *>(&o1) = z;
+              *reinterpret_cast<uint4 *>(&o2) = z; *reinterpret_cast<uint4 *>(&o3) = z;
+            }
             // 64-byte swizzle: 16-byte chunk index XOR ((row >> 1) & 3)
             const uint32_t off = (uint32_t)row * 64u + (uint32_t)((v ^ ((row >> 1) & 3)) << 4);
             *reinterpret_cast<uint4 *>(slab + off) = *reinterpret_cast<const uint4 *>(&o0);
