@@ -43,7 +43,7 @@ __device__ unsigned int g_row_error = 0;
 #ifdef WINO_ROW_TRACE
 // Development aid (not built by default): per-role accumulated wait clocks of CTA 0.
 __device__ unsigned long long g_row_trace[32];
-__device__ unsigned long long g_row_tl[10][256];     // event timeline of CTA 0: [role][event index] = clock64
+__device__ unsigned long long g_row_tl[12][256];     // event timeline of CTA 0: [role][event index] = clock64
 #ifdef WINO_ROW_TL
 #define TL(role, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_row_tl[role][idx] = (unsigned long long)clock64(); } while (0)
 #else
@@ -440,6 +440,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           for (int ch = 0; ch < g.n_chunks; ++ch) {
             const int s = it & 1;
             if (!mbar_wait_warp(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
+            if (lane == 0) TL(10, it);
             if (ROW_DBG(g, 2u)) { if (lane == 0) mbar_arrive(raw_full(s)); ++it; continue; }
             if (lane == 0) {
               mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
@@ -1174,7 +1175,7 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
 #ifdef WINO_ROW_TRACE
 extern "C" __attribute__((visibility("default"))) int winoconv_debug_row_timeline(unsigned long long *out) {
   cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, g_row_tl, sizeof(unsigned long long) * 10 * 256);
+  return (int)cudaMemcpyFromSymbol(out, g_row_tl, sizeof(unsigned long long) * 12 * 256);
 }
 extern "C" __attribute__((visibility("default"))) int winoconv_debug_row_trace(unsigned long long *out, int clear) {
   cudaDeviceSynchronize();
