@@ -1,9 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own Python code.
 
-Run in a container that has the reference checkout (default ``/root/reference``; override with
-``WINOCONV_REFERENCE_DIR``):
+Run where a checkout of the reference project is available, pointing ``WINOCONV_REFERENCE_DIR`` at it:
 
-    python tests/golden/make_golden.py
+    WINOCONV_REFERENCE_DIR=<reference checkout> python tests/golden/make_golden.py
 
 It imports the only two reference modules that run on CPU -- ``wincnn`` (the vendored
 Cook-Toom generator) and ``matrix_convnd`` (``conv`` / ``base_conv32``, matrix_convnd.py:99-153)
@@ -24,7 +23,8 @@ import warnings
 import numpy as np
 import torch
 
-REF = os.environ.get("WINOCONV_REFERENCE_DIR", "/root/reference")
+HERE_EARLY = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("WINOCONV_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE_EARLY))), "reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

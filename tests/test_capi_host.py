@@ -35,7 +35,7 @@ BASELINE_CONFIGS = [
 
 
 @pytest.mark.parametrize("name,kw,expect", BASELINE_CONFIGS)
-def test_plan_matches_survey_figures(name, kw, expect):
+def test_plan_matches_hand_computed_figures(name, kw, expect):
     info = capi.plan(capi.make_desc(**kw))
     assert (info.positions, info.n_pieces, info.tiles) == expect
     d = capi.make_desc(**kw)
