@@ -41,10 +41,10 @@ if ROOT not in sys.path:
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
-# summarised under profiles/ (None until a capture exists for that kernel and workload).
+# kept with the profile summaries (None until a capture exists for that kernel and workload).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
     # rowfused_kernel, C = K = 256 at 56 x 56 (VGG layers 6-7): 169.1 MB at N = 64 in the capture of
-    # profiles/rowfused_pair_c256_k256_56_ncu.md, scaled to the bench's N = 256 (traffic is proportional to N;
+    # the paired kernel's profile summary, scaled to the bench's N = 256 (traffic is proportional to N;
     # algorithmic bytes of that layer at N = 256: 824 MB, part of y is still dirty in L2 when the kernel ends)
     ("vgg16", "rowfused_kernel"): 676.4e6,
 }
