@@ -996,6 +996,18 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
     fixed = 2 * raw_bytes + n_a * a_bytes + 2048;
   }
   int nb = (budget - fixed) / b_stage;
+  // One channel block whose whole item's filter slabs would fit the ring if a slab set gave up its room: keeping the
+  // filter resident (loaded once per CTA) beats the third slab set (a 7x7 stride-2 layer run as 4x4 over 12
+  // channels has 8 stages per item: four fit beside three slab sets, eight beside two).
+  const int stages_per_item = p.n_chunks * d.kD * d.kH * p.PW;
+  if (p.n_nblocks == 1 && n_a == 3 && nb < stages_per_item && stages_per_item <= 8) {
+    const int fixed2 = 2 * raw_bytes + 2 * a_bytes + 2048;
+    if ((budget - fixed2) / b_stage >= stages_per_item) {
+      n_a = 2;
+      fixed = fixed2;
+      nb = (budget - fixed) / b_stage;
+    }
+  }
   if (nb < 2) return false;
   if (nb > 8) nb = 8;
   p.n_a_bufs = n_a;
