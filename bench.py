@@ -607,7 +607,7 @@ def run_ours(args):
         "e2e": {"value": round(e2e_value, 2), "unit": "images/s", "ms_per_step": round(ms_e2e / args.steps, 4),
                 "h2d_bytes_per_step": int(x_host.numel() * x_host.element_size() * world),
                 "d2h_bytes_per_step": int(y_host.numel() * y_host.element_size() * world)},
-        "gpu_launches": int(model.launches_per_call * args.steps),
+        "gpu_launches": int(model.launches_per_call * args.steps * world),   # all ranks, timed region of `value`
         "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": clocks, "layers": per_layer,
     }
     print(json.dumps(line), flush=True)
