@@ -33,6 +33,8 @@ SMALL = [
     (1, 4, 4, (4, 9, 9), (1, 3, 3), 1, 1, 0),    # depth kernel of 1 in a 3-D tensor
     (1, 4, 4, (7, 8, 9), (3, 3, 3), 2, 1, 0),    # 3-D stride 2
     (1, 4, 4, (12, 4, 4), (10, 3, 3), 1, 1, 0),  # 10 -> 3+3+3+1
+    (1, 4, 4, (7, 10, 11), (5, 7, 7), 1, 0, 0),  # asymmetric 3-D shapes of the reference's piece table: 18 pieces
+    (1, 4, 4, (10, 7, 8), (8, 4, 4), 1, 0, 0),   # 8 -> 3+3+2, 4 -> 2+2: 12 pieces
 ]
 
 
