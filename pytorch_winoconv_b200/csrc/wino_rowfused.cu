@@ -828,30 +828,41 @@ struct PhaseGeom {
 };
 template <typename T>
 __global__ void __launch_bounds__(256) phases_to_channels_kernel(const T *__restrict__ x, T *__restrict__ xs, PhaseGeom q) {
-  const int groups = q.Cp / 8;
+  const unsigned groups = (unsigned)(q.Cp / 8);
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long pixels = (long long)q.N * q.D * q.H * q.W;
   if (idx >= pixels * groups) return;
-  long long px = idx / groups;
+  const long long px = idx / groups;
   const int cg = (int)(idx - px * groups) * 8;
-  const int iw = (int)(px % q.W); px /= q.W;
-  const int ih = (int)(px % q.H); px /= q.H;
-  const int id = (int)(px % q.D);
-  const int n = (int)(px / q.D);
+  // pixel coordinates: one 64-bit division by the row length, the rest in 32 bits
+  const long long row = px / q.W;
+  const int iw = (int)(px - row * q.W);
+  const unsigned rowu = (unsigned)row;                  // N * D * H rows: fits 32 bits for any tensor that fits memory
+  const unsigned ndh = rowu / (unsigned)q.H;
+  const int ih = (int)(rowu - ndh * (unsigned)q.H);
+  const int n = (int)(ndh / (unsigned)q.D);
+  const int id = (int)(ndh - (unsigned)n * (unsigned)q.D);
   const int C = q.fD * q.fH * q.fW * q.C0;
+  // channel c = phase * C0 + c0 is walked incrementally: one division for the first channel of the group
+  int phase = cg / q.C0, c0 = cg - phase * q.C0;
+  const T *src = nullptr;                                // first channel of the current phase's source pixel, or null
+  bool fresh = true;
   __align__(16) T v[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int c = cg + i;
     T val = T(0.f);
-    if (c < C) {
-      int phase = c / q.C0;
-      const int c0 = c - phase * q.C0;
-      const int pw = phase % q.fW; phase /= q.fW;
-      const int ph = phase % q.fH; phase /= q.fH;
-      const int sd = q.fD * id + phase - q.pD0, sh = q.fH * ih + ph - q.pH0, sw = q.fW * iw + pw - q.pW0;
-      if (sd >= 0 && sd < q.D0 && sh >= 0 && sh < q.H0 && sw >= 0 && sw < q.W0)
-        val = x[((((long long)n * q.D0 + sd) * q.H0 + sh) * q.W0 + sw) * q.C0 + c0];
+    if (cg + i < C) {
+      if (fresh) {
+        const int pw = phase % q.fW, t = phase / q.fW;
+        const int ph = t % q.fH, pd = t / q.fH;
+        const int sd = q.fD * id + pd - q.pD0, sh = q.fH * ih + ph - q.pH0, sw = q.fW * iw + pw - q.pW0;
+        src = (sd >= 0 && sd < q.D0 && sh >= 0 && sh < q.H0 && sw >= 0 && sw < q.W0)
+                  ? x + ((((long long)n * q.D0 + sd) * q.H0 + sh) * q.W0 + sw) * q.C0
+                  : nullptr;
+        fresh = false;
+      }
+      if (src) val = src[c0];
+      if (++c0 == q.C0) { c0 = 0; ++phase; fresh = true; }
     }
     v[i] = val;
   }
