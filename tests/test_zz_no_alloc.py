@@ -12,11 +12,11 @@ pytestmark = pytest.mark.gpu
 TOL = {torch.float16: 2e-2, torch.float32: 1e-3}     # the E_B bounds of tests/gpu_util.py
 
 
-def _layer(seed, n, c, k, hw, ks, pad, dtype, tile_m=0):
+def _layer(seed, n, c, k, hw, ks, pad, dtype, tile_m=0, stride=1):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(n, hw, hw, c, generator=g).to(dtype).cuda()
     w = (torch.randn(k, c, ks, ks, generator=g) * (2.0 / (c * ks * ks)) ** 0.5).to(dtype).cuda()
-    conv = engine.WinoConv(x.shape, w, padding=pad, tile_m=tile_m)
+    conv = engine.WinoConv(x.shape, w, stride=stride, padding=pad, tile_m=tile_m)
     return x, conv
 
 
@@ -44,6 +44,17 @@ def test_static_scratch_forward_matches_on_consecutive_calls():
     assert need_a > capi.STATIC_SCRATCH_BYTES            # so the array is reused within one call
     errs = [_both(xa, ca), _both(xb, cb), _both(xa, ca)]
     print("forward_static vs forward, E_B:", errs)
+
+
+def test_static_scratch_serves_the_single_kernel_paths():
+    # the row kernel's only scratch: channel padding (3 -> 8) and the stride-2 phase gather (4 x 3 -> 16 channels)
+    xa, ca = _layer(3, 4, 3, 32, 40, 3, 1, torch.float16)
+    xb, cb = _layer(4, 4, 3, 32, 41, 7, 3, torch.float16, stride=2)
+    assert ca.info.algo == capi.ALGO_ROW and cb.info.algo == capi.ALGO_ROW
+    assert 0 < int(ca.info.input_ws_bytes) <= capi.STATIC_SCRATCH_BYTES
+    assert 0 < int(cb.info.input_ws_bytes) <= capi.STATIC_SCRATCH_BYTES
+    errs = [_both(xa, ca), _both(xb, cb), _both(xa, ca)]
+    print("forward_static vs forward (row kernel), E_B:", errs)
 
 
 def test_static_scratch_refuses_oversized_layers():
