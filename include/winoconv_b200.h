@@ -57,8 +57,10 @@ typedef enum winoconv_algo {
   WINOCONV_ALGO_STAGED = 1, /* input transform -> batched GEMM -> output transform through V / M scratch  */
   WINOCONV_ALGO_FUSED = 2,  /* one tcgen05 kernel, 3x3 pieces as F(2x2,3x3); f16 / bf16, any stride       */
   WINOCONV_ALGO_ROW = 3     /* one tcgen05 kernel, 1x3 pieces: F(2,3) along W, taps along H / depth summed */
-                            /* in TMEM; f16 / bf16, stride 1, kernel <= 7 taps tall.  Scratch only to pad  */
-                            /* the channels of x to a multiple of 8 (v_ws, winoconv_plan: input_ws_bytes)  */
+                            /* in TMEM; f16 / bf16, strides 1 or 2 (stride 2 runs as a stride-1 problem    */
+                            /* over phase channels), kernel <= 7 taps tall (14 at stride 2).  Scratch only */
+                            /* to pad the channels of x to a multiple of 8 or to hold the phase-gathered   */
+                            /* input (v_ws, winoconv_plan: input_ws_bytes)                                 */
 } winoconv_algo_t;
 
 /* epilogue bits, applied inside the output transform */

@@ -32,7 +32,8 @@ Matrix = List[List[Fraction]]
 
 # Interpolation points used by the reference for each (m, r) it tabulates
 # (matrix_conv.py:31-40).  F(4,3) is not tabulated there; (0, 1, -1, 2, -2) is the
-# customary choice and the one the engine's device code uses.
+# customary choice and what the reference's generator would be fed (the engine's device
+# code uses ENGINE_F43_POINTS below instead).
 _LONG_POINTS = (0, 1, -1, Fraction(1, 2), -Fraction(1, 2), Fraction(1, 3), -Fraction(1, 3),
                 Fraction(3, 2), -Fraction(3, 2), -3, 2, -2)
 

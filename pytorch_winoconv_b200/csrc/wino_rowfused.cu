@@ -1,4 +1,5 @@
-// Row-piece DWM forward for f16 / bf16, stride 1, on sm_100a: the kernel is decomposed the DWM way into
+// Row-piece DWM forward for f16 / bf16 on sm_100a (stride 1; the caller presents stride 2 as a stride-1 problem over
+// phase channels, see RowDesc): the kernel is decomposed the DWM way into
 // 1 x 3 pieces -- along W every run of three taps is a Winograd F(2,3) window (zero taps where the kernel
 // ends), along H (and depth) every tap is its own piece, for which F(m,1) is the identity.  All pieces write
 // the same four Winograd positions of a tile of 1 x 2 outputs, so they are summed where the GEMM accumulates:
@@ -39,19 +40,6 @@
 namespace wino {
 
 __device__ unsigned int g_row_error = 0;
-
-#ifdef WINO_ROW_TRACE
-// Development aid (not built by default): per-role accumulated wait clocks of CTA 0.
-__device__ unsigned long long g_row_trace[32];
-__device__ unsigned long long g_row_tl[12][256];     // event timeline of CTA 0: [role][event index] = clock64
-#ifdef WINO_ROW_TL
-#define TL(role, idx) do { if (blockIdx.x == 0 && (idx) < 256) g_row_tl[role][idx] = (unsigned long long)clock64(); } while (0)
-#else
-#define TL(role, idx) do { } while (0)
-#endif
-#else
-#define TL(role, idx) do { } while (0)
-#endif
 
 namespace rowf {
 
@@ -105,9 +93,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
-#ifdef WINO_ROW_TRACE
-  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_row_trace[code & 15u], (unsigned long long)(clock64() - start));
-#endif
   return true;
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
@@ -241,12 +226,6 @@ struct Smem {
   int total;
 };
 
-// Timing ablations exist in development builds only; in the shipped library every switch is the constant false.
-#ifdef WINO_ROW_TRACE
-#define ROW_DBG(g_, bit_) (((g_).dbg & (bit_)) != 0u)
-#else
-#define ROW_DBG(g_, bit_) false
-#endif
 
 struct RGeom {
   int N, C, K;
@@ -263,7 +242,6 @@ struct RGeom {
   int n_nblocks;
   long long n_items;
   unsigned epilogue;
-  unsigned dbg;           // development builds only (WINO_ROW_TRACE): 2 no input TMA, 4 no transform, 8 no MMA, 16 no stores
 };
 
 template <typename T, int BN, int MB, bool PAIR>
@@ -292,9 +270,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + sl.off_bars + 516);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef WINO_ROW_TRACE
-  const long long trace_kernel_t0 = clock64();
-#endif
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(raw_full(i), 1);
@@ -386,8 +361,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           for (int ch = 0; ch < g.n_chunks; ++ch) {
             const int s = it & 1;
             if (!mbar_wait_warp(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
-            if (lane == 0) TL(10, it);
-            if (ROW_DBG(g, 2u)) { if (lane == 0) mbar_arrive(raw_full(s)); ++it; continue; }
             if (lane == 0) {
               mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
               tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
@@ -414,7 +387,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         if (lane == 0) ok = mbar_wait(raw_full(rs), (it_raw >> 1) & 1u, abort_word, ERR_PROD_RAW) ? 1u : 0u;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (ok == 0u) { alive = false; break; }
-        if (ptid == 0) TL(8, it_raw);
         const uint8_t *raw = base_ptr + sl.off_raw[rs];
         // A slab with at most 16 real channels (few-channel input, phase-gathered RGB, the tail of C) is read by the
         // MMAs through one K = 16 step, i.e. the first two 16-byte vectors of each row: only those are produced, and
@@ -429,10 +401,9 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           if (lane == 0) ok = mbar_wait(a_empty(as), a_par, abort_word, ERR_PROD_A) ? 1u : 0u;
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (ok == 0u) { alive = false; break; }
-          if (ptid == 0) TL(4, it_a);
           uint8_t *slab = base_ptr + sl.off_a[as];
           const int slab_bytes = g.slab_rows * 64;
-          for (int row = ptid >> vshift; row < (ROW_DBG(g, 4u) ? 0 : n_tasks); row += N_PROD >> vshift) {
+          for (int row = ptid >> vshift; row < n_tasks; row += N_PROD >> vshift) {
             const int ir = row >> cbw_shift, cp = row - (ir << cbw_shift);
             V8<T> o0, o1, o2, o3;
             if (real) {
@@ -458,7 +429,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // each writer: its stores before the MMA's reads
           __syncwarp();
           if (lane == 0) { if (PAIR) mbar_arrive_rank0(a_full(as)); else mbar_arrive(a_full(as)); }
-          if (ptid == 0) TL(5, it_a);
           ++it_a;
           if (++as == sl.n_a_bufs) { as = 0; a_par ^= 1u; }
         }
@@ -485,7 +455,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             for (int w = 0; w < g.PW && alive; ++w)
               for (int kh = 0; kh < g.kH; ++kh) {
                 if (!mbar_wait_warp(b_empty(s), s_par, abort_word, ERR_B_EMPTY)) { alive = false; break; }
-                if (lane == 0) TL(2, it);
                 const int slab0 = ((kd * g.kH + kh) * g.PW + w) * 4;
                 if (lane != 0) {
                   // only lane 0 issues
@@ -501,7 +470,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
                   for (int j = 0; j < 4; ++j)
                     tma_load_3d(dst + j * (BN * 64), &map_u, b_full(s), ch * KC, nb * BN, slab0 + j);
                 }
-                if (lane == 0) TL(3, it);
                 ++it;
                 dst += (uint32_t)sl.b_stage_bytes;
                 if (++s == nbs) { s = 0; s_par ^= 1u; dst = base + sl.off_b; }
@@ -525,14 +493,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 #define MMA_COMMIT(bar_) do { if (lane == 0) { if (PAIR) umma_commit_pair(bar_); else umma_commit(bar_); } } while (0)
       uint32_t it_a = 0, it_b = 0, n_done = 0;
       bool alive = true;
-#ifdef WINO_ROW_TRACE
-      // LAP(k): clocks since the previous LAP are charged to segment k (register accumulators, written once)
-      unsigned lap_t = (unsigned)clock();
-      unsigned lap_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-#define LAP(k) do { if (half == 0) { const unsigned now_ = (unsigned)clock(); lap_acc[k] += now_ - lap_t; lap_t = now_; } } while (0)
-#else
-#define LAP(k) do { } while (0)
-#endif
       // Everything the loop needs per stage is kept incrementally (ring position, parity, descriptor, barrier address):
       // this one thread feeds the tensor pipe, and a division or a descriptor rebuild per stage shows up as idle MMA time.
       const uint32_t slab16 = (uint32_t)(g.slab_rows * 64 / 16);
@@ -549,39 +509,29 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       const int tail_chunk = (g.Cp - (g.n_chunks - 1) * KC > UMMA_K) ? -1 : g.n_chunks - 1;   // chunk with one K step only
       const int kH = g.kH, PW = g.PW, n_chunks = g.n_chunks;   // loop bounds in registers
       const long long n_items = g.n_items;
-      const bool skip_mma = ROW_DBG(g, 8u);
       const uint32_t a_half16 = (uint32_t)half * slab16, b_half16 = (uint32_t)half * B_SLAB16;
       for (long long item = item0; item < n_items && alive; item += item_step, ++n_done) {
         const int ab = (ACC_BUFS == 2) ? (int)(n_done & 1u) : 0;
         const uint32_t use = (ACC_BUFS == 2) ? (n_done >> 1) : n_done;
-        LAP(6);
         if (!MMA_WAIT(acc_empty(ab), (use & 1u) ^ 1u, abort_word, ERR_MMA_ACC)) { alive = false; break; }
-        LAP(7);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem_base + (uint32_t)(ab * ACC_COLS);
         uint32_t acc0 = 0u;
         int ch = 0;
         for (int step = 0; step < steps_per_item && alive; ++step) {
           // a slab with at most 16 real channels (few-channel input, or the tail of C) needs one K = 16 step only
-          LAP(14);
           const bool k2 = ch != tail_chunk;
           if (++ch == n_chunks) ch = 0;
-          LAP(15);
           for (int w = 0; w < PW && alive; ++w) {
-            LAP(9);
             if (!MMA_WAIT(a_full((int)as), a_par, abort_word, ERR_MMA_A)) { alive = false; break; }
-            LAP(5);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (lane == 0) TL(9, it_a);
             uint32_t a_lo_kh = (as == 0 ? a_lo_buf0 : (as == 1 ? a_lo_buf1 : a_lo_buf2)) + a_half16;
             // one stage = one filter row kh: straight-line code for the usual three rows (a taken branch costs this
             // lone warp ~100 clocks of instruction fetch)
             auto do_stage = [&]() -> bool {
-              LAP(0);
               if (!(b_resident && n_done > 0))
                 if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) return false;
-              LAP(1); if (lane == 0) TL(0, it_b);
-              if (!skip_mma && lane == 0) {
+              if (lane == 0) {
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
                   const uint32_t a_lo = a_lo_kh + (uint32_t)(mb * BM * 4);      // block mb starts RB * CBW = 128 rows later
@@ -592,14 +542,11 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
                 }
               }
               acc0 = 1u;
-              LAP(3); if (lane == 0) TL(1, it_b);
               if (!b_resident) MMA_COMMIT(b_empty((int)bs));
-              LAP(4);
               ++it_b;
               a_lo_kh += kh_step16;
               b_lo0 += b_stage16;
               if (++bs == b_ring) { bs = 0; b_lo0 = b_lo_base; b_par = b_resident ? 0u : (b_par ^ 1u); }
-              LAP(2);
               return true;
             };
             if (kH == 3) {
@@ -608,25 +555,16 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
               for (int kh = 0; kh < kH && alive; ++kh) alive = do_stage();
               if (!alive) break;
             }
-            LAP(8);
             MMA_COMMIT(a_empty((int)as));
-            LAP(6);
             ++it_a;
             if (++as == n_a) { as = 0; a_par ^= 1u; }
-            LAP(11);
-            LAP(12);
           }
-          LAP(13);
         }
         MMA_COMMIT(acc_full(ab));
-        LAP(10);
       }
 #undef MMA_WAIT
 #undef MMA_ISSUE
 #undef MMA_COMMIT
-#ifdef WINO_ROW_TRACE
-      if (blockIdx.x == 0 && half == 0 && lane == 0) for (int k = 0; k < 16; ++k) g_row_trace[16 + k] = lap_acc[k];
-#endif
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -641,7 +579,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
     const bool pool = (g.epilogue & WINOCONV_EPI_POOL2) != 0;
     // widest store the output allows: 32 bytes (K % 16, 32-byte aligned base), 16 bytes (K % 8), or elements
     const int st_mode = ((g.K % 16) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0) ? 2 : ((g.K % 8) == 0 ? 1 : 0);
-    const bool no_store = ROW_DBG(g, 16u);
     const int K = g.K;
     constexpr int C_PER_WARP = BN / 2;
     uint32_t n_done = 0;
@@ -655,7 +592,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
       if (lane == 0) got = mbar_wait(acc_full(ab), use & 1u, abort_word, ERR_EPI) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (got == 0u) { alive = false; break; }
-      if (warp == EPI_WARP0 && lane == 0) TL(6, n_done);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int ow = (cb * g.CBW + tcp) * 2;
       const int k0 = nb * BN + chalf * C_PER_WARP;      // first output channel of this warp
@@ -669,11 +605,11 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         if (pool) {
           const int ph = oh >> 1, pw = ow >> 1;
           dst = y + ((((long long)n * g.oD + od) * g.yH + ph) * g.yW + pw) * K + k0;
-          st0 = (tr & 1) == 0 && ph < g.yH && pw < g.yW && n < g.N && !no_store;
+          st0 = (tr & 1) == 0 && ph < g.yH && pw < g.yW && n < g.N;
           st1 = false;
         } else {
           dst = y + ((((long long)n * g.oD + od) * g.oH + oh) * g.oW + ow) * K + k0;
-          const bool in = oh < g.oH && n < g.N && !no_store;
+          const bool in = oh < g.oH && n < g.N;
           st0 = in && ow < g.oW;
           st1 = in && ow + 1 < g.oW;
         }
@@ -693,7 +629,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
               asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
               __syncwarp();
               if (lane == 0) { if (PAIR) mbar_arrive_rank0(acc_empty(ab)); else mbar_arrive(acc_empty(ab)); }
-              if (warp == EPI_WARP0 && lane == 0) TL(7, n_done);
             }
             const int kbase = k0 + cc;
             float y0[8], y1[8];
@@ -741,12 +676,6 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (PAIR) cluster_sync_all();   // neither CTA frees tensor memory or exits while the other may still use it
-#ifdef WINO_ROW_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    g_row_trace[0] += (unsigned long long)(clock64() - trace_kernel_t0);
-    g_row_trace[15] += (unsigned long long)((g.n_items + gridDim.x - 1) / gridDim.x);
-  }
-#endif
   if (warp == MMA_WARP0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
@@ -888,8 +817,9 @@ static EncodeTiledFn get_encode_fn() {
 
 }  // namespace rowf
 
-// Fills the geometry of the row-piece kernel for this convolution; returns false when it does not apply
-// (stride 2, kernel taller than 7, or a patch / slab that does not fit shared memory).
+// Fills the geometry of the row-piece kernel for the stride-1 problem in `d` (a stride-2 convolution arrives here
+// already folded into phase channels); returns false when it does not apply (kernel taller than 7, or a patch /
+// slab that does not fit shared memory).
 bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   using namespace rowf;
   if (d.sD != 1 || d.sH != 1 || d.sW != 1) return false;
@@ -1017,12 +947,6 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   g.PW = p.PW; g.RB = p.RB; g.CBW = p.CBW; g.MB = p.MB; g.n_rb = p.n_rb; g.n_cb = p.n_cb; g.slab_rows = p.slab_rows;
   g.patch_h = p.patch_h; g.patch_w = p.patch_w; g.n_chunks = p.n_chunks; g.n_nblocks = p.n_nblocks;
   g.n_items = p.n_items; g.epilogue = d.epilogue;
-#ifdef WINO_ROW_TRACE
-  static const unsigned dbg = [] { const char *v = getenv("WINOCONV_ROW_DBG"); return v && *v ? (unsigned)atoi(v) : 0u; }();
-  g.dbg = dbg;
-#else
-  g.dbg = 0u;
-#endif
   Smem sl;
   sl.raw_bytes = p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
   sl.a_bytes = p.a_bytes; sl.b_stage_bytes = p.b_stage_bytes; sl.n_b_stages = p.n_b_stages;
@@ -1141,21 +1065,6 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
 #undef ROWF_DISPATCH
 }
 
-#ifdef WINO_ROW_TRACE
-extern "C" __attribute__((visibility("default"))) int winoconv_debug_row_timeline(unsigned long long *out) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, g_row_tl, sizeof(unsigned long long) * 12 * 256);
-}
-extern "C" __attribute__((visibility("default"))) int winoconv_debug_row_trace(unsigned long long *out, int clear) {
-  cudaDeviceSynchronize();
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_row_trace, sizeof(unsigned long long) * 32);
-  if (e == cudaSuccess && clear) {
-    unsigned long long z[32] = {};
-    e = cudaMemcpyToSymbol(g_row_trace, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
 
 cudaError_t read_and_clear_row_error(cudaStream_t s, unsigned int *code) {
   unsigned int host = 0, zero = 0;

@@ -239,7 +239,7 @@ def test_cfg4_fp16_3d(algo, name):
     print("cfg4 engine", name, check_against_oracle(x, w, y, padding=1))
 
 
-def test_auto_resolves_to_fused_for_16bit_f2_and_staged_otherwise():
+def test_auto_resolves_to_row_for_16bit_and_staged_otherwise():
     x = seeded((1, 8, 12, 12), 1, dtype=torch.float16)
     w5 = wo.kaiming_normal((8, 8, 5, 5), 2).half()
     w3 = wo.kaiming_normal((8, 8, 3, 3), 3).half()
