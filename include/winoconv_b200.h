@@ -186,7 +186,11 @@ WINOCONV_API int winoconv_forward_timed(const winoconv_desc_t *desc, const void 
  * cudaMalloc, cudaFree or any allocating library routine.
  *   - Limit: 128 tiles of scratch (winoconv_plan: input_ws_bytes_min + product_ws_bytes_min) must fit the
  *     array; larger layers are refused with WINOCONV_ERR_WORKSPACE and a message stating both sizes.
- *     Layers that fit are walked in as many passes as the array allows.
+ *     Layers that fit are walked in as many passes as the array allows.  A ROW layer uses the array for
+ *     its whole channel-padded or phase-gathered copy of the input (winoconv_plan: input_ws_bytes; e.g. a
+ *     3 -> 64 layer at 224 x 224 passes 32 MiB from batch 41 on) and is refused the same way beyond that:
+ *     the transformed filter is laid out per algorithm, so re-plan that layer with algo =
+ *     WINOCONV_ALGO_FUSED (no scratch at all) or WINOCONV_ALGO_STAGED, transform its filter again and call.
  *   - The first call on each device looks up the array's device address (with that device current) and
  *     keeps it; make that first call before starting any stream capture.
  *   - All calls on a device share the one array, and it keeps whatever the previous call left.  Nothing

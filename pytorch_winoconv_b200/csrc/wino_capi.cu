@@ -518,8 +518,11 @@ int winoconv_forward_static(const winoconv_desc_t *desc, const void *x, const vo
     return forward_impl(desc, x, u, bias, y, nullptr, 0, nullptr, 0, stream, nullptr, nullptr);
   if (plan.row) {   // the built-in array serves as the channel-padding buffer
     if (I.input_ws_bytes_min > WINOCONV_STATIC_SCRATCH_BYTES)
-      return fail(WINOCONV_ERR_WORKSPACE, "padding the input channels needs " + std::to_string(I.input_ws_bytes_min) +
-                                              " bytes; the built-in array holds " + std::to_string(WINOCONV_STATIC_SCRATCH_BYTES));
+      return fail(WINOCONV_ERR_WORKSPACE, "the row kernel's channel-padded / phase-gathered copy of the input needs " +
+                                              std::to_string(I.input_ws_bytes_min) + " bytes; the built-in array holds " +
+                                              std::to_string(WINOCONV_STATIC_SCRATCH_BYTES) +
+                                              " (plan and filter-transform this layer with algo = WINOCONV_ALGO_FUSED, which needs"
+                                              " no scratch, or WINOCONV_ALGO_STAGED, and call again)");
     unsigned char *pad = nullptr;
     if ((st = static_scratch_of_current_device(&pad)) != WINOCONV_OK) return st;
     return forward_impl(desc, x, u, bias, y, pad, WINOCONV_STATIC_SCRATCH_BYTES, nullptr, 0, stream, nullptr, nullptr);

@@ -48,12 +48,17 @@ class ScratchPool:
 
     Kernels of consecutive layers run on one stream, so sharing is safe; callers using several
     streams on one device should give each its own pool (``WinoConv(..., pool=ScratchPool())``).
+
+    A block that is outgrown is kept, not freed: a CUDA graph captured earlier holds its raw address
+    (``VGG16ConvStack.capture``), and handing the block back to the caching allocator would let a later
+    tensor land on memory the graph still reads and writes on replay.
     """
     _default: Dict[int, "ScratchPool"] = {}
 
     def __init__(self):
         self.v: Optional[torch.Tensor] = None
         self.m: Optional[torch.Tensor] = None
+        self._outgrown: List[torch.Tensor] = []
 
     @classmethod
     def default(cls, device: torch.device) -> "ScratchPool":
@@ -62,8 +67,12 @@ class ScratchPool:
 
     def get(self, device, v_bytes: int, m_bytes: int) -> Tuple[torch.Tensor, torch.Tensor]:
         if self.v is None or self.v.numel() < v_bytes or self.v.device != device:
+            if self.v is not None:
+                self._outgrown.append(self.v)
             self.v = torch.empty(v_bytes, dtype=torch.uint8, device=device)
         if self.m is None or self.m.numel() < m_bytes or self.m.device != device:
+            if self.m is not None:
+                self._outgrown.append(self.m)
             self.m = torch.empty(m_bytes, dtype=torch.uint8, device=device)
         return self.v, self.m
 

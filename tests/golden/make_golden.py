@@ -15,6 +15,11 @@ Fixtures:
   cooktoom_golden.npz      AT/G/BT for the (points, m, r) the reference tabulates
                            (matrix_conv.py:31-40) plus F(4,3) on (0,1,-1,2,-2)
   tile_algebra_golden.npz  matrix_convnd.conv outputs for 1-D/2-D/3-D tiles, r in {1,2,3,5,7}
+  split_control_golden.npz the piece boxes of every kernel shape in the reference's splitControl()
+                           look-up table (src/base_conv_launchers.h:58-388), read from the source text:
+                           shapes [n,3] = (kD,kH,kW), offsets [n+1], boxes [sum pieces, 6] =
+                           (D_s, D_e, H_s, H_e, W_s, W_e); a branch's piece count is the length of its
+                           D_s array, as the C code computes it (`sizeof(D_s) / sizeof(D_s[0])`)
 """
 import os
 import sys
@@ -38,6 +43,25 @@ def _install_sympy_shim():
         return orig(self, other)
 
     MatrixBase.__truediv__ = truediv
+
+
+def parse_split_control(header_path):
+    """[( (kD,kH,kW), [(D_s,D_e,H_s,H_e,W_s,W_e), ...] ), ...] from the text of splitControl()."""
+    import re
+    text = open(header_path).read()
+    text = text[text.index("static void splitControl"):]
+    out = []
+    branches = re.split(r"if ?\(D == (\d+) && H == (\d+) && W == (\d+)\)", text)
+    for i in range(1, len(branches), 4):
+        shape = tuple(int(v) for v in branches[i:i + 3])
+        body = branches[i + 3]
+        arrs = {}
+        for name in ("D_s", "D_e", "H_s", "H_e", "W_s", "W_e"):
+            m = re.search(r"int %s\[\] = \{([^}]*)\}" % name, body)
+            arrs[name] = [int(v) for v in m.group(1).split(",")]
+        n = len(arrs["D_s"])
+        out.append((shape, [tuple(arrs[k][j] for k in ("D_s", "D_e", "H_s", "H_e", "W_s", "W_e")) for j in range(n)]))
+    return out
 
 
 def main():
@@ -81,6 +105,11 @@ def main():
         y = matrix_convnd.conv(x.clone(), w.clone(), n)          # [T, K, 2, ...]
         blob[f"{name}_x"], blob[f"{name}_w"], blob[f"{name}_y"] = x.numpy(), w.numpy(), y.numpy()
     np.savez_compressed(os.path.join(HERE, "tile_algebra_golden.npz"), **blob)
+    lut = parse_split_control(os.path.join(REF, "src", "base_conv_launchers.h"))
+    shapes = np.array([sh for sh, _ in lut], dtype=np.int64)
+    offsets = np.cumsum([0] + [len(b) for _, b in lut]).astype(np.int64)
+    boxes = np.array([b for _, bs in lut for b in bs], dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "split_control_golden.npz"), shapes=shapes, offsets=offsets, boxes=boxes)
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

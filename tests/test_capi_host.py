@@ -114,6 +114,32 @@ def test_piece_table_matches_oracle_rule(ks, stride):
     assert got == want
 
 
+def _split_control_golden():
+    import os
+    import numpy as np
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "split_control_golden.npz"))
+    for i, shape in enumerate(d["shapes"].tolist()):
+        yield tuple(shape), [tuple(b) for b in d["boxes"][d["offsets"][i]:d["offsets"][i + 1]].tolist()]
+
+
+def test_piece_table_reproduces_every_box_of_the_reference_lut():
+    """All 36 kernel shapes of splitControl() (src/base_conv_launchers.h:58-388), read from the reference's source
+    by tests/golden/make_golden.py: the library's rule and the oracle's rule give the same boxes in the same order."""
+    n = 0
+    for shape, boxes in _split_control_golden():
+        if shape[0] == 1:
+            d = capi.make_desc(ndim=2, batch=1, c_in=8, k_out=8, in_size=(16, 16), ker_size=shape[1:], tile_m=2)
+        else:
+            d = capi.make_desc(ndim=3, batch=1, c_in=8, k_out=8, in_size=(16, 16, 16), ker_size=shape, tile_m=2)
+        got = [(st[0], st[0] + r[0], st[1], st[1] + r[1], st[2], st[2] + r[2]) for ph, st, r in capi.plan_pieces(d)]
+        assert all(ph == (0, 0, 0) for ph, _, _ in capi.plan_pieces(d))
+        assert got == boxes, (shape, got, boxes)
+        want = wo.dwm_pieces(shape, (1, 1, 1))
+        assert [(p[0][1], p[0][1] + p[0][2], p[1][1], p[1][1] + p[1][2], p[2][1], p[2][1] + p[2][2]) for p in want] == boxes, shape
+        n += 1
+    assert n == 36
+
+
 def test_piece_table_3d():
     d = capi.make_desc(ndim=3, batch=1, c_in=8, k_out=8, in_size=(12, 12, 12), ker_size=(5, 7, 7))
     got = capi.plan_pieces(d)

@@ -197,13 +197,14 @@ def test_cfg1_fp32_f23():
 
 
 @pytest.mark.parametrize("product_dtype", [None, torch.float16])
-def test_cfg2_fp16_f43(product_dtype):
-    x = seeded((32, 256, 28, 28), 0, dtype=torch.float16)
-    w = wo.kaiming_normal((256, 256, 3, 3), 1).half()
+@pytest.mark.parametrize("seed", [0, 17])
+def test_cfg2_fp16_f43(product_dtype, seed):
+    x = seeded((32, 256, 28, 28), seed, dtype=torch.float16)
+    w = wo.kaiming_normal((256, 256, 3, 3), seed + 1).half()
     y, conv = run_engine(x, w, padding=1, tile_m=4, product_dtype=product_dtype)
     assert conv.info.positions == 36 and conv.info.gemm_engine == capi.GEMM_TCGEN05
     err = check_against_oracle(x, w, y, padding=1)
-    print("cfg2 engine", product_dtype, err)
+    print("cfg2 engine", product_dtype, "seed", seed, err)
 
 
 ALGOS = [(capi.ALGO_STAGED, "staged"), (capi.ALGO_FUSED, "fused"), (capi.ALGO_ROW, "row")]

@@ -37,7 +37,7 @@ def test_vgg16_stack_matches_float64_stack():
         if i in wo.VGG16_POOL_AFTER:
             ref = torch.nn.functional.max_pool2d(ref, 2)
         e = wo.error_metrics(out.permute(0, 3, 1, 2).cpu(), ref)
-        assert e["E_A"] < 1e-2, (i, e)
+        assert e["E_A"] < 1e-2 and e["E_B"] <= 2e-2, (i, e)     # the fp16 gate of every other config, per layer
         h = out.clone()
     # CUDA-graph replay gives the same bits as eager
     stack.capture(xl)
@@ -63,3 +63,27 @@ def test_vgg16_stack_staged_f43_matches_float64_stack():
     err = wo.error_metrics(y, wo.vgg16_conv_stack_f64(x, ws))
     print("vgg16 staged F(4,3) stack error vs float64", err)
     assert err["E_A"] < 3e-2, err
+
+
+def test_graph_replay_survives_growth_of_the_shared_scratch_pool():
+    """A captured stack holds raw scratch addresses; a larger layer run later on the same device makes the
+    shared pool grow, and the replay must still read and write memory that is its own."""
+    batch = 1
+    x = torch.rand(batch, 3, 224, 224, generator=torch.Generator().manual_seed(3)).half()
+    ws = _weights(torch.float16)
+    stack = engine.VGG16ConvStack([w.cuda() for w in ws], batch, tile_m=4, algo=capi.ALGO_STAGED)
+    xl = x.permute(0, 2, 3, 1).contiguous().cuda()
+    stack.capture(xl)
+    y0 = stack.replay(xl).clone()
+    pool = engine.ScratchPool.default(xl.device)
+    before = (pool.v.data_ptr(), pool.v.numel())
+    big_x = torch.randn(8, 224, 224, 64, generator=torch.Generator().manual_seed(4)).half().cuda()
+    big = engine.WinoConv(big_x.shape, ws[1].cuda(), padding=1, tile_m=4, algo=capi.ALGO_STAGED)
+    big(big_x)
+    filler = [torch.full((before[1],), 0x5A, dtype=torch.uint8, device=xl.device) for _ in range(3)]   # would reuse a freed block
+    assert pool.v.numel() > before[1] and any(t.data_ptr() == before[0] for t in pool._outgrown)
+    y1 = stack.replay(xl)
+    torch.cuda.synchronize()
+    assert capi.read_device_error() == 0
+    assert torch.equal(y0, y1)
+    del filler

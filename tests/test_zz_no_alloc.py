@@ -5,6 +5,7 @@ Collected last on purpose (file name), and self-contained so it also passes alon
 import pytest
 import torch
 
+from oracle import winograd_oracle as wo
 from pytorch_winoconv_b200 import capi, engine
 
 pytestmark = pytest.mark.gpu
@@ -17,6 +18,7 @@ def _layer(seed, n, c, k, hw, ks, pad, dtype, tile_m=0, stride=1):
     x = torch.randn(n, hw, hw, c, generator=g).to(dtype).cuda()
     w = (torch.randn(k, c, ks, ks, generator=g) * (2.0 / (c * ks * ks)) ** 0.5).to(dtype).cuda()
     conv = engine.WinoConv(x.shape, w, stride=stride, padding=pad, tile_m=tile_m)
+    conv.test_w, conv.test_stride, conv.test_pad = w, stride, pad
     return x, conv
 
 
@@ -32,6 +34,10 @@ def _both(x, conv):
     rms = y_ref.double().pow(2).mean().sqrt()
     e_b = (d / torch.maximum(y_ref.double().abs(), rms)).max().item()
     assert e_b <= TOL[x.dtype], e_b
+    # and against the float64 direct convolution of the same rounded inputs, so the check stands by itself
+    o = wo.direct_conv_f64(x.permute(0, 3, 1, 2).cpu(), conv.test_w.cpu(), stride=conv.test_stride, padding=conv.test_pad)
+    err = wo.error_metrics(y.permute(0, 3, 1, 2).cpu(), o)
+    assert err["E_B"] <= TOL[x.dtype], err
     return e_b
 
 
@@ -64,3 +70,13 @@ def test_static_scratch_refuses_oversized_layers():
         capi.forward_static(d, 256, 256, None, 256)
     assert ei.value.status == capi.ERR_WORKSPACE
     assert "33554432" in str(ei.value)
+
+
+def test_static_scratch_refuses_an_oversized_row_layer_and_names_the_way_out():
+    # 3 -> 64 at 224 x 224, batch 64: the row kernel's 8-channel copy of the input is 51 MB > 32 MiB
+    d = capi.make_desc(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=3, pad=1)
+    assert capi.plan(d).algo == capi.ALGO_ROW and capi.plan(d).input_ws_bytes > capi.STATIC_SCRATCH_BYTES
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.forward_static(d, 256, 256, None, 256)
+    assert ei.value.status == capi.ERR_WORKSPACE
+    assert "WINOCONV_ALGO_FUSED" in str(ei.value) and "33554432" in str(ei.value)
