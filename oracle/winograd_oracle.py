@@ -82,16 +82,24 @@ def direct_conv_numpy(x: np.ndarray, w: np.ndarray, stride=1, padding=0) -> np.n
 # --------------------------------------------------------------------------------------
 # error metrics
 # --------------------------------------------------------------------------------------
-def error_metrics(y: torch.Tensor, oracle: torch.Tensor) -> dict:
+def error_metrics(y: torch.Tensor, oracle: torch.Tensor, percentile: bool = False) -> dict:
     """E_B gates: max |y-o| / max(|o|, rms(o)).  E_A = max|d|/max|o|, E_C = mean(|d|/|o|)
-    (the quantity the reference prints, example.py:105-108)."""
+    (the quantity the reference prints, example.py:105-108; taken over the non-zero oracle values, since
+    a ReLU output has exact zeros).  ``percentile`` adds P999, the 99.9th percentile of the E_B ratio."""
     yd, od = y.detach().cpu().double(), oracle.detach().cpu().double()
     d = (yd - od).abs()
     rms = od.pow(2).mean().sqrt().clamp_min(1e-300)
-    e_b = (d / torch.maximum(od.abs(), rms)).max().item()
+    ratio = d / torch.maximum(od.abs(), rms)
+    e_b = ratio.max().item()
     e_a = (d.max() / od.abs().max().clamp_min(1e-300)).item()
-    e_c = (d / od.abs().clamp_min(1e-300)).mean().item()
-    return {"E_B": e_b, "E_A": e_a, "E_C": e_c}
+    nz = od != 0
+    e_c = (d[nz] / od[nz].abs()).mean().item() if bool(nz.any()) else 0.0
+    out = {"E_B": e_b, "E_A": e_a, "E_C": e_c}
+    if percentile:
+        flat = ratio.flatten()
+        kth = max(1, int(math.ceil(0.999 * flat.numel())))
+        out["P999"] = torch.kthvalue(flat, kth).values.item()
+    return out
 
 
 # --------------------------------------------------------------------------------------

@@ -369,6 +369,12 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             ++it;
           }
       }
+      // After an abort nobody consumes the patches still in flight: let them land (bounded) before the CTA can exit.
+      if (*abort_word != 0u && lane == 0)
+        for (uint32_t back = 1; back <= 2u && back <= it; ++back) {
+          const uint32_t j = it - back;
+          for (int polls = 0; polls < (1 << 16) && !mbar_try_wait(raw_full((int)(j & 1u)), (j >> 1) & 1u); ++polls) { }
+        }
     }
   } else if (warp < B_WARP) {
     // ---------------------------------------------------------------- F(2,3) along W: raw patch -> four slabs
@@ -475,6 +481,9 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
                 if (++s == nbs) { s = 0; s_par ^= 1u; dst = base + sl.off_b; }
               }
       }
+      // After an abort the filter slabs still in flight must land before the CTA may exit and free its shared memory.
+      // Their bytes are counted on rank 0's barriers, which the other CTA of a pair cannot poll: a fixed delay of a
+      // millisecond (a TMA load takes microseconds) covers every case.
       if (*abort_word != 0u) {
         const long long start = clock64();
         while (clock64() - start < 2000000LL) { }

@@ -199,7 +199,7 @@ class VGG16ConvStack:
 
     def __init__(self, weights: Sequence[torch.Tensor], batch: int, height: int = 224, width: int = 224,
                  tile_m: int = 0, product_dtype: Optional[torch.dtype] = None, gemm_engine: int = capi.GEMM_AUTO,
-                 algo: int = capi.ALGO_AUTO):
+                 algo: int = capi.ALGO_AUTO, pool: Optional[ScratchPool] = None):
         if len(weights) != 13:
             raise ValueError("VGG-16 has 13 convolutions")
         self.layers: List[WinoConv] = []
@@ -211,7 +211,7 @@ class VGG16ConvStack:
             cin = int(wt.shape[1])
             conv = WinoConv((batch, h, w, cin), wt, padding=1, tile_m=tile_m, relu=True,
                             pool2=i in VGG16_POOL_AFTER, product_dtype=product_dtype, gemm_engine=gemm_engine,
-                            algo=algo)
+                            algo=algo, pool=pool)
             self.layers.append(conv)
             self.acts.append(torch.empty(conv.out_shape, dtype=dt, device=dev))
             h, w = conv.out_shape[1], conv.out_shape[2]

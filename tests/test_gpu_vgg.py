@@ -71,14 +71,14 @@ def test_graph_replay_survives_growth_of_the_shared_scratch_pool():
     batch = 1
     x = torch.rand(batch, 3, 224, 224, generator=torch.Generator().manual_seed(3)).half()
     ws = _weights(torch.float16)
-    stack = engine.VGG16ConvStack([w.cuda() for w in ws], batch, tile_m=4, algo=capi.ALGO_STAGED)
+    pool = engine.ScratchPool()                      # its own pool, so earlier tests cannot have grown it already
+    stack = engine.VGG16ConvStack([w.cuda() for w in ws], batch, tile_m=4, algo=capi.ALGO_STAGED, pool=pool)
     xl = x.permute(0, 2, 3, 1).contiguous().cuda()
     stack.capture(xl)
     y0 = stack.replay(xl).clone()
-    pool = engine.ScratchPool.default(xl.device)
     before = (pool.v.data_ptr(), pool.v.numel())
     big_x = torch.randn(8, 224, 224, 64, generator=torch.Generator().manual_seed(4)).half().cuda()
-    big = engine.WinoConv(big_x.shape, ws[1].cuda(), padding=1, tile_m=4, algo=capi.ALGO_STAGED)
+    big = engine.WinoConv(big_x.shape, ws[1].cuda(), padding=1, tile_m=4, algo=capi.ALGO_STAGED, pool=pool)
     big(big_x)
     filler = [torch.full((before[1],), 0x5A, dtype=torch.uint8, device=xl.device) for _ in range(3)]   # would reuse a freed block
     assert pool.v.numel() > before[1] and any(t.data_ptr() == before[0] for t in pool._outgrown)
