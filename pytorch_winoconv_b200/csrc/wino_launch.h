@@ -50,6 +50,7 @@ struct RowPlan {
   int Cp, PW, BN, MB, CBW, RB, n_rb, n_cb, slab_rows, patch_h, patch_w, n_chunks, n_nblocks, slabs;
   long long filter_elems, n_items;
   int raw_bytes, a_bytes, b_stage_bytes, n_b_stages, n_a_bufs, smem_total;
+  int b_group;   // filter stages per barrier group (1, or 3 = all rows of a 3-row kernel)
   int pair;   // 1: CTA pairs (two images per work item, one M = 256 MMA over both SMs, filter slabs split between them)
 };
 bool rowfused_plan(const RowDesc &d, RowPlan *out);

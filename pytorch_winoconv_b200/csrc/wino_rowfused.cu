@@ -222,6 +222,7 @@ __device__ __forceinline__ void store16p(T *dst, const uint32_t (&pk)[8], int kb
 struct Smem {
   int raw_bytes, a_bytes, b_stage_bytes;   // one raw patch; one set of four slabs; one stage of four filter slabs
   int n_b_stages, n_a_bufs;
+  int b_group;                             // filter stages per full / empty barrier pair (1, or all kH rows of a window)
   int off_raw[2], off_a[3], off_b, off_bars;
   int total;
 };
@@ -446,11 +447,13 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
   } else if (warp == B_WARP) {
     // ---------------------------------------------------------------- transformed-filter slabs
     {
-      uint32_t it = 0;
       bool alive = true;
-      const int nbs = sl.n_b_stages;
-      int s = 0;
-      uint32_t s_par = 1u;                          // parity of the "stage is free" wait: first round passes
+      // Stages are handed over in groups of `gk` consecutive filter rows (one or all kH): one wait and one expected
+      // byte count per group here, one wait and one commit per group in each MMA warp.
+      const int gk = sl.b_group;
+      const int n_groups = sl.n_b_stages / gk;
+      int s = 0;                                    // group slot
+      uint32_t s_par = 1u;                          // parity of the "group is free" wait: first round passes
       uint32_t dst = base + sl.off_b;
       ItemWalk wk = make_walk();
       for (long long item = item0; item < g.n_items && alive; item += item_step, wk.advance()) {
@@ -459,26 +462,28 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         for (int kd = 0; kd < g.kD && alive; ++kd)
           for (int ch = 0; ch < g.n_chunks && alive; ++ch)
             for (int w = 0; w < g.PW && alive; ++w)
-              for (int kh = 0; kh < g.kH; ++kh) {
+              for (int kh0 = 0; kh0 < g.kH; kh0 += gk) {
                 if (!mbar_wait_warp(b_empty(s), s_par, abort_word, ERR_B_EMPTY)) { alive = false; break; }
-                const int slab0 = ((kd * g.kH + kh) * g.PW + w) * 4;
-                if (lane != 0) {
-                  // only lane 0 issues
-                } else if (PAIR) {   // this CTA's half (BN / 2 rows) of each slab; rank 0 expects the bytes of both halves
-                  if (rank == 0) mbar_expect_tx(b_full(s), 2u * (uint32_t)sl.b_stage_bytes);
+                if (lane == 0) {
+                  if (!PAIR || rank == 0)   // rank 0 of a pair expects the bytes of both halves
+                    mbar_expect_tx(b_full(s), (PAIR ? 2u : 1u) * (uint32_t)(gk * sl.b_stage_bytes));
+                  for (int kh = kh0; kh < kh0 + gk; ++kh) {
+                    const int slab0 = ((kd * g.kH + kh) * g.PW + w) * 4;
+                    if (PAIR) {             // this CTA's half (BN / 2 rows) of each slab
 #pragma unroll
-                  for (int j = 0; j < 4; ++j)
-                    tma_load_3d_pair(dst + j * (BN / 2 * 64), &map_u, b_full(s), ch * KC,
-                                     nb * BN + (int)rank * (BN / 2), slab0 + j);
-                } else {
-                  mbar_expect_tx(b_full(s), (uint32_t)sl.b_stage_bytes);
+                      for (int j = 0; j < 4; ++j)
+                        tma_load_3d_pair(dst + j * (BN / 2 * 64), &map_u, b_full(s), ch * KC,
+                                         nb * BN + (int)rank * (BN / 2), slab0 + j);
+                    } else {
 #pragma unroll
-                  for (int j = 0; j < 4; ++j)
-                    tma_load_3d(dst + j * (BN * 64), &map_u, b_full(s), ch * KC, nb * BN, slab0 + j);
+                      for (int j = 0; j < 4; ++j)
+                        tma_load_3d(dst + j * (BN * 64), &map_u, b_full(s), ch * KC, nb * BN, slab0 + j);
+                    }
+                    dst += (uint32_t)sl.b_stage_bytes;
+                  }
                 }
-                ++it;
-                dst += (uint32_t)sl.b_stage_bytes;
-                if (++s == nbs) { s = 0; s_par ^= 1u; dst = base + sl.off_b; }
+                dst = __shfl_sync(0xffffffffu, dst, 0);
+                if (++s == n_groups) { s = 0; s_par ^= 1u; dst = base + sl.off_b; }
               }
       }
       // After an abort the filter slabs still in flight must land before the CTA may exit and free its shared memory.
@@ -500,14 +505,15 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 #define MMA_WAIT(bar_, par_, aw_, code_) mbar_wait(bar_, par_, aw_, code_)   /* every lane polls; lanes differ only when a wait gives up */
 #define MMA_ISSUE(d_, a_, b_, i_, acc_) do { if (PAIR) umma_f16_lohi_pair(d_, a_, b_, i_, acc_); else umma_f16_lohi(d_, a_, b_, i_, acc_); } while (0)   /* inside if (lane == 0) */
 #define MMA_COMMIT(bar_) do { if (lane == 0) { if (PAIR) umma_commit_pair(bar_); else umma_commit(bar_); } } while (0)
-      uint32_t it_a = 0, it_b = 0, n_done = 0;
+      uint32_t n_done = 0;
       bool alive = true;
       // Everything the loop needs per stage is kept incrementally (ring position, parity, descriptor, barrier address):
       // this one thread feeds the tensor pipe, and a division or a descriptor rebuild per stage shows up as idle MMA time.
       const uint32_t slab16 = (uint32_t)(g.slab_rows * 64 / 16);
       constexpr uint32_t B_SLAB16 = (uint32_t)((PAIR ? BN / 2 : BN) * 64 / 16);   // a CTA of a pair holds half the rows
       static_assert(KC / UMMA_K == 2, "two K = 16 steps per slab");
-      const uint32_t b_ring = b_resident ? (uint32_t)(steps_per_item * g.PW * g.kH) : (uint32_t)sl.n_b_stages;
+      const int gk = sl.b_group;                          // filter rows per barrier group
+      const uint32_t b_ring = (b_resident ? (uint32_t)(steps_per_item * g.PW * g.kH) : (uint32_t)sl.n_b_stages) / (uint32_t)gk;
       const uint32_t b_stage16 = (uint32_t)(sl.b_stage_bytes >> 4);
       const uint32_t b_lo_base = desc_lo(base + sl.off_b);
       uint32_t bs = 0, b_par = 0, b_lo0 = b_lo_base;
@@ -535,11 +541,10 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             if (!MMA_WAIT(a_full((int)as), a_par, abort_word, ERR_MMA_A)) { alive = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t a_lo_kh = (as == 0 ? a_lo_buf0 : (as == 1 ? a_lo_buf1 : a_lo_buf2)) + a_half16;
-            // one stage = one filter row kh: straight-line code for the usual three rows (a taken branch costs this
-            // lone warp ~100 clocks of instruction fetch)
-            auto do_stage = [&]() -> bool {
-              if (!(b_resident && n_done > 0))
-                if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) return false;
+            // one group = gk filter rows behind one full / empty barrier pair: one wait, 2 gk MMAs back to back, one commit.
+            // Straight-line code for the usual three rows (a taken branch costs this lone warp ~100 clocks of
+            // instruction fetch); whatever this warp does besides issuing is time its position's MMAs are not queued.
+            auto issue_row = [&]() {
               if (lane == 0) {
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
@@ -551,21 +556,39 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
                 }
               }
               acc0 = 1u;
-              if (!b_resident) MMA_COMMIT(b_empty((int)bs));
-              ++it_b;
               a_lo_kh += kh_step16;
               b_lo0 += b_stage16;
-              if (++bs == b_ring) { bs = 0; b_lo0 = b_lo_base; b_par = b_resident ? 0u : (b_par ^ 1u); }
+            };
+            auto group_begin = [&]() -> bool {
+              if (!(b_resident && n_done > 0))
+                if (!mbar_wait(b_full((int)bs), b_par, abort_word, ERR_MMA_B)) return false;
               return true;
             };
-            if (kH == 3) {
-              if (!do_stage() || !do_stage() || !do_stage()) { alive = false; break; }
+            auto group_end = [&]() {
+              if (!b_resident) MMA_COMMIT(b_empty((int)bs));
+              if (++bs == b_ring) { bs = 0; b_lo0 = b_lo_base; b_par = b_resident ? 0u : (b_par ^ 1u); }
+            };
+            if (gk == 3) {          // kH == 3, all three rows in one group
+              if (!group_begin()) { alive = false; break; }
+              issue_row(); issue_row(); issue_row();
+              group_end();
+            } else if (kH == 3) {   // gk == 1
+              bool ok = group_begin();
+              if (ok) { issue_row(); group_end(); ok = group_begin(); }
+              if (ok) { issue_row(); group_end(); ok = group_begin(); }
+              if (ok) { issue_row(); group_end(); }
+              if (!ok) { alive = false; break; }
             } else {
-              for (int kh = 0; kh < kH && alive; ++kh) alive = do_stage();
+              for (int kh0 = 0; kh0 < kH && alive; kh0 += gk) {
+                alive = group_begin();
+                if (alive) {
+                  for (int j = 0; j < gk; ++j) issue_row();
+                  group_end();
+                }
+              }
               if (!alive) break;
             }
             MMA_COMMIT(a_empty((int)as));
-            ++it_a;
             if (++as == n_a) { as = 0; a_par ^= 1u; }
           }
         }
@@ -906,6 +929,23 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   }
   if (nb < 2) return false;
   if (nb > 8) nb = 8;
+  // Streamed 3-row kernels: hand the filter over in groups of all three rows (one barrier round trip per 32-channel
+  // step and MMA warp instead of three) when two such groups fit the ring, giving up the third slab set if that is
+  // what it takes.  WINOCONV_ROW_BGROUP=1 keeps single-row stages.
+  static const int bgroup_env = [] { const char *v = getenv("WINOCONV_ROW_BGROUP"); return v && *v ? atoi(v) : 0; }();
+  p.b_group = 1;
+  const bool resident = p.n_nblocks == 1 && stages_per_item <= nb;
+  if (d.kH == 3 && !resident && bgroup_env != 1) {
+    int n_a_g = n_a;
+    int room = (budget - (2 * raw_bytes + n_a_g * a_bytes + 2048)) / b_stage;
+    if (room < 6 && n_a_g == 3) { n_a_g = 2; room = (budget - (2 * raw_bytes + n_a_g * a_bytes + 2048)) / b_stage; }
+    if (room >= 6) {
+      p.b_group = 3;
+      n_a = n_a_g;
+      fixed = 2 * raw_bytes + n_a * a_bytes + 2048;
+      nb = 6;
+    }
+  }
   p.n_a_bufs = n_a;
   p.raw_bytes = raw_bytes; p.a_bytes = a_bytes; p.b_stage_bytes = b_stage; p.n_b_stages = nb;
   p.smem_total = fixed + nb * b_stage;
@@ -960,6 +1000,7 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   sl.raw_bytes = p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
   sl.a_bytes = p.a_bytes; sl.b_stage_bytes = p.b_stage_bytes; sl.n_b_stages = p.n_b_stages;
   sl.n_a_bufs = p.n_a_bufs;
+  sl.b_group = p.b_group;
   sl.off_a[0] = 0;                                                 // slabs first: 1024-byte aligned
   sl.off_a[1] = p.n_a_bufs >= 2 ? p.a_bytes : 0;
   sl.off_a[2] = p.n_a_bufs >= 3 ? 2 * p.a_bytes : 0;
