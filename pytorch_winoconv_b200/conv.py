@@ -15,15 +15,27 @@ stride 2 included, no cuDNN branch.  What the reference pays per call and these 
 * separate bias / ReLU / max-pool passes: ``activation="relu"`` and ``pool=2`` run in the
   convolution's epilogue.
 
-Forward only, as upstream: a call that would need a gradient raises.  ``groups != 1`` and dilation
-raise too (the reference accepts ``groups`` and silently computes groups = 1).
+Backward (the reference left only traces of one: ``include/splitstrideone/split_functions_grad.h:1-7``,
+``backwardAssign`` at ``src/back/utils.cu:16``) runs on the engine's kernels too:
+
+* data gradient: the forward engine on the flipped, transposed filter -- ``grad_x = conv(grad_y, flip(w)^T)``
+  with padding ``k - 1 - p``; a stride-2 layer first spreads ``grad_y`` onto the stride grid (zeros between);
+* weight gradient: one tensor-core GEMM per filter tap, ``dW[:, :, tap] = grad_y^T  x_shifted(tap)`` with the
+  batch and output pixels as the reduction (``winoconv_gemm_batched``, fp32 accumulate);
+* bias gradient: a sum.
+
+A fused ReLU is differentiated through the stored output; the fused max-pool is forward only.
+``groups != 1`` and dilation raise (the reference accepts ``groups`` and silently computes groups = 1).
 """
 from __future__ import annotations
 
+import itertools
+import math
 from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from . import capi, engine
 
@@ -82,8 +94,14 @@ class _WinoConvMixin:
         if not input.is_cuda:
             raise RuntimeError("the Winograd engine runs on CUDA devices only: there is no CPU or cuDNN path")
         if torch.is_grad_enabled() and (input.requires_grad or self.weight.requires_grad and self.training):
-            raise NotImplementedError("forward only: call under torch.no_grad() / module.eval() "
-                                      "(the reference has no backward pass either)")
+            if self.pool:
+                raise NotImplementedError("the fused max-pool is forward only: use pool=None and a separate "
+                                          "torch.nn.MaxPool2d where a gradient is needed")
+            return _WinoConvFn.apply(self, input, self.weight, self.bias)
+        return self._forward_no_grad(input)
+
+    def _forward_no_grad(self, input: torch.Tensor) -> torch.Tensor:      # noqa: A002
+        nd = self._nd
         dtype = self.compute_dtype if self.compute_dtype is not None else input.dtype
         x = input.detach()
         if x.dtype != dtype:
@@ -97,6 +115,75 @@ class _WinoConvMixin:
         y_cl = plan(x_cl)
         # NCHW-shaped view of the channels-last result (torch.channels_last memory format): no copy
         return y_cl.permute(0, nd + 1, *range(1, nd + 1))
+
+    # -- backward ----------------------------------------------------------------------------------
+    def _grad_input(self, gy_cl: torch.Tensor, in_shape_cl: Tuple[int, ...]) -> torch.Tensor:
+        """grad_x, channels last, from the channels-last ``grad_y`` in the compute dtype."""
+        nd = self._nd
+        ks = tuple(int(k) for k in self.weight.shape[2:])
+        st = tuple(int(v) for v in self.stride)
+        pd = tuple(int(v) for v in self.padding)
+        in_sp = in_shape_cl[1:-1]
+        left = [k - 1 - p for k, p in zip(ks, pd)]
+        if min(left) < 0:
+            raise NotImplementedError("data gradient needs padding <= kernel - 1")
+        extra = [(n + 2 * p - k) % s for n, p, k, s in zip(in_sp, pd, ks, st)]     # input rows the strided forward never read
+        z = gy_cl
+        if any(s > 1 for s in st):       # spread grad_y onto the stride grid
+            full = [(o - 1) * s + 1 for o, s in zip(gy_cl.shape[1:-1], st)]
+            z = gy_cl.new_zeros((gy_cl.shape[0], *full, gy_cl.shape[-1]))
+            z[(slice(None), *[slice(None, None, s) for s in st], slice(None))] = gy_cl
+        pad_arg = tuple(left)
+        if any(extra) or any(s > 1 for s in st):
+            spec = [0, 0]
+            for l, e in zip(reversed(left), reversed(extra)):
+                spec += [l, l + e]
+            z = F.pad(z, spec).contiguous()
+            pad_arg = (0,) * nd
+        key = ("bwd", tuple(z.shape), z.dtype, z.device)
+        wkey = self._current_weight_key(z.dtype, z.device)
+        if wkey != self._weight_key:
+            self._plans.clear()
+            self._weight_key = wkey
+        plan = self._plans.get(key)
+        if plan is None:
+            wt = self.weight.detach().to(device=z.device, dtype=z.dtype).flip(*range(2, 2 + nd)).transpose(0, 1).contiguous()
+            plan = engine.WinoConv(tuple(z.shape), wt, stride=1, padding=pad_arg)
+            self._plans[key] = plan
+        gx = plan(z)
+        assert tuple(gx.shape) == tuple(in_shape_cl), (gx.shape, in_shape_cl)
+        return gx
+
+    def _grad_weight(self, gy_cl: torch.Tensor, x_cl: torch.Tensor) -> torch.Tensor:
+        """dW [K, C, *k] in fp32: per filter tap, grad_y^T [K, R] times the shifted input [R, C] on the engine's
+        batched GEMM (R = batch x output pixels, zero-extended to a multiple of 8)."""
+        nd = self._nd
+        ks = tuple(int(k) for k in self.weight.shape[2:])
+        st = tuple(int(v) for v in self.stride)
+        pd = tuple(int(v) for v in self.padding)
+        n, out_sp, k_out = int(gy_cl.shape[0]), tuple(int(v) for v in gy_cl.shape[1:-1]), int(gy_cl.shape[-1])
+        c_in = int(x_cl.shape[-1])
+        r = n * math.prod(out_sp)
+        rp = (r + 7) // 8 * 8
+        dcode = engine.dtype_code(gy_cl.dtype)
+        spec = [0, 0]
+        for p in reversed(pd):
+            spec += [p, p]
+        xp = F.pad(x_cl, spec)
+        gyt = gy_cl.new_zeros((k_out, rp))
+        gyt[:, :r] = gy_cl.reshape(r, k_out).t()
+        xt = x_cl.new_zeros((c_in, rp))
+        dw = torch.empty((k_out, c_in, *ks), dtype=torch.float32, device=gy_cl.device)
+        m = torch.empty((k_out, c_in), dtype=torch.float32, device=gy_cl.device)
+        stream = torch.cuda.current_stream(gy_cl.device).cuda_stream
+        with torch.cuda.device(gy_cl.device):
+            for tap in itertools.product(*[range(k) for k in ks]):
+                win = (slice(None), *[slice(t, t + (o - 1) * s + 1, s) for t, o, s in zip(tap, out_sp, st)], slice(None))
+                xt[:, :r] = xp[win].reshape(r, c_in).t()
+                capi.gemm_batched(dcode, capi.F32, capi.GEMM_AUTO, 1, k_out, rp, c_in, gyt.data_ptr(), xt.data_ptr(),
+                                  m.data_ptr(), stream)
+                dw[(slice(None), slice(None), *tap)] = m
+        return dw
 
     def extra_repr(self) -> str:
         s = super().extra_repr()
@@ -112,6 +199,39 @@ class _WinoConvMixin:
         """Algorithm the engine chose for every input shape seen so far: {shape: 'row' | 'fused' | 'staged'}."""
         names = {capi.ALGO_ROW: "row", capi.ALGO_FUSED: "fused", capi.ALGO_STAGED: "staged"}
         return {shape: names.get(int(p.info.algo), str(p.info.algo)) for shape, p in self._plans.items()}
+
+
+class _WinoConvFn(torch.autograd.Function):
+    """Autograd node of the module forward: every arithmetic kernel of the three gradients is the engine's."""
+
+    @staticmethod
+    def forward(ctx, module, x, weight, bias):
+        y = module._forward_no_grad(x)
+        ctx.module = module
+        ctx.save_for_backward(x, y if module.activation == "relu" else None)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        module = ctx.module
+        x, y = ctx.saved_tensors
+        nd = module._nd
+        dtype = module.compute_dtype if module.compute_dtype is not None else x.dtype
+        perm_in = (0, *range(2, 2 + nd), 1)
+        to_nchw = (0, nd + 1, *range(1, nd + 1))
+        if y is not None:
+            gy = gy * (y > 0).to(gy.dtype)
+        gy_cl = gy.detach().to(dtype).permute(*perm_in).contiguous()
+        x_cl = x.detach().to(dtype).permute(*perm_in).contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[1]:
+            gx = module._grad_input(gy_cl, tuple(int(v) for v in x_cl.shape)).permute(*to_nchw).to(x.dtype)
+        if ctx.needs_input_grad[2]:
+            gw = module._grad_weight(gy_cl, x_cl).to(module.weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            gb = gy_cl.float().sum(dim=tuple(range(0, nd + 1))).to(module.bias.dtype)
+        return None, gx, gw, gb
 
 
 class Conv2d(_WinoConvMixin, nn.Conv2d):

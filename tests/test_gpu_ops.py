@@ -141,8 +141,17 @@ def test_matrix_conv3d_and_nd_and_dwm_convnd():
     wk = seeded((8, 8, 3, 3), 41)
     got = matrix_convnd.base_conv32(tiles.cuda(), wk.cuda(), False, 2, [3, 3], 2).cpu()
     assert (got.double() - wo.base_conv(tiles.double(), wk.double(), [2, 2])).abs().max().item() < 1e-4
-    with pytest.raises(NotImplementedError):
-        matrix_convnd.base_conv32(torch.zeros(1, 8, 4, 4, 4, 4).cuda(), torch.zeros(8, 8, 3, 3, 3, 3).cuda(), False, 2, [3] * 4, 4)
+    # n > 3 (matrix_convnd.py:110-153, convnd.py:156-195): 4-D and 5-D tiles against the sliding-window float64 oracle
+    # and against the oracle's restatement of the reference's n-D tile algebra
+    for n, r in ((4, 3), (5, 3), (4, 5)):
+        xt = seeded((3, 8) + (r + 1,) * n, 50 + n)
+        wt = seeded((8, 8) + (r,) * n, 60 + n + r) * (1.0 / (8 * r ** n)) ** 0.5
+        o = torch.from_numpy(wo.direct_conv_numpy(xt.numpy(), wt.numpy()))
+        y = (dwm_convnd.conv32 if r > 3 else matrix_convnd.conv32)(xt.cuda(), wt.cuda(), n).cpu()
+        assert tuple(y.shape) == (3, 8) + (2,) * n
+        assert wo.error_metrics(y, o)["E_B"] < 1e-3
+        if r == 3:
+            assert wo.error_metrics(y, wo.base_conv(xt.double(), wt.double(), [2] * n))["E_B"] < 1e-3
 
 
 def test_wino_class():

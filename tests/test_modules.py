@@ -85,11 +85,72 @@ def test_channels_last_io_is_zero_copy_and_cache_follows_the_weight():
     assert wo.error_metrics(y2.cpu().double(), 2.0 * o)["E_A"] < 5e-3
 
 
+def _grads_f64(x, w, b, gy, stride, pad, relu):
+    """float64 torch.autograd.grad of F.conv2d / conv3d on the same rounded tensors."""
+    xd, wd = x.double().requires_grad_(True), w.double().requires_grad_(True)
+    bd = None if b is None else b.double().requires_grad_(True)
+    conv = torch.nn.functional.conv2d if w.dim() == 4 else torch.nn.functional.conv3d
+    y = conv(xd, wd, bd, stride=stride, padding=pad)
+    if relu:
+        y = torch.relu(y)
+    return torch.autograd.grad(y, [xd, wd] + ([bd] if bd is not None else []), gy.double())
+
+
 @pytest.mark.gpu
-def test_training_mode_call_that_needs_grad_raises():
-    m = wconv.Conv2d(8, 8, 3, padding=1).cuda()
-    x = torch.randn(1, 8, 8, 8, device="cuda")
+@pytest.mark.parametrize("shape", [
+    # n, c, k, hw, kernel, stride, pad, relu
+    (4, 32, 48, 20, 3, 1, 1, False),
+    (2, 16, 24, 18, 5, 1, 2, True),
+    (2, 8, 16, 23, 7, 2, 3, False),          # stride 2, and (23 + 6 - 7) % 2 == 0
+    (2, 8, 16, 24, 3, 2, 1, False),          # stride 2 with an input row the forward never reads
+])
+def test_backward_matches_float64_autograd(shape):
+    n, c, k, hw, ks, stride, pad, relu = shape
+    torch.manual_seed(11)
+    m = wconv.Conv2d(c, k, ks, stride=stride, padding=pad, bias=True, activation="relu" if relu else None).cuda()
+    x = torch.randn(n, c, hw, hw).half()
+    xg = x.cuda().requires_grad_(True)
+    y = m(xg)
+    gy = torch.randn(y.shape, generator=torch.Generator().manual_seed(12)).half()
+    y.backward(gy.cuda())
+    w16, b16 = m.weight.detach().cpu().half(), m.bias.detach().cpu().half()
+    gx, gw, gb = _grads_f64(x, w16, b16, gy, stride, pad, relu)
+    # the ReLU mask of the engine's fp16 output can differ from the float64 one where y is within rounding of zero
+    tol = 2e-2 if not relu else 4e-2
+    assert wo.error_metrics(xg.grad.cpu(), gx)["E_B"] < tol
+    assert wo.error_metrics(m.weight.grad.cpu(), gw)["E_B"] < tol
+    assert wo.error_metrics(m.bias.grad.cpu(), gb)["E_B"] < tol
+
+
+@pytest.mark.gpu
+def test_data_gradient_at_the_baseline_shapes():
+    """grad_x of configs[1] (3x3, 256 -> 256 at 28 x 28) and configs[2]b (5x5, 128 -> 128 at 56 x 56) against float64."""
+    for n, c, k, hw, ks, pad in [(32, 256, 256, 28, 3, 1), (8, 128, 128, 56, 5, 2)]:
+        torch.manual_seed(13)
+        m = wconv.Conv2d(c, k, ks, padding=pad, bias=False).cuda().eval()
+        x = torch.randn(n, c, hw, hw).half()
+        xg = x.cuda().requires_grad_(True)
+        y = m(xg)
+        gy = torch.randn(y.shape, generator=torch.Generator().manual_seed(14)).half()
+        (gx,) = torch.autograd.grad(y, [xg], gy.cuda())
+        ref = _grads_f64(x, m.weight.detach().cpu().half(), None, gy, 1, pad, False)[0]
+        assert wo.error_metrics(gx.cpu(), ref)["E_B"] < 2e-2
+
+
+@pytest.mark.gpu
+def test_conv3d_backward_and_pool_refusal():
+    torch.manual_seed(15)
+    m = wconv.Conv3d(8, 8, 3, padding=1, bias=False).cuda()
+    x = torch.randn(1, 8, 6, 9, 10).half()
+    xg = x.cuda().requires_grad_(True)
+    y = m(xg)
+    gy = torch.randn(y.shape, generator=torch.Generator().manual_seed(16)).half()
+    y.backward(gy.cuda())
+    gx, gw = _grads_f64(x, m.weight.detach().cpu().half(), None, gy, 1, 1, False)
+    assert wo.error_metrics(xg.grad.cpu(), gx)["E_B"] < 2e-2
+    assert wo.error_metrics(m.weight.grad.cpu(), gw)["E_B"] < 2e-2
+    mp = wconv.Conv2d(8, 8, 3, padding=1, pool=2).cuda()
     with pytest.raises(NotImplementedError):
-        m(x)                                                              # train mode, grad enabled
+        mp(torch.randn(1, 8, 8, 8, device="cuda"))                        # train mode: the fused pool has no gradient
     with torch.no_grad():
-        assert tuple(m(x).shape) == (1, 8, 8, 8)
+        assert tuple(mp(torch.randn(1, 8, 8, 8, device="cuda")).shape) == (1, 8, 4, 4)
