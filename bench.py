@@ -74,8 +74,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4", "conv"],
-                    help="vgg16 = BASELINE configs[4] (the headline); cfg1..cfg4 = the single-layer configs[0..3]; conv = --shape")
+    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4", "conv", "gemm"],
+                    help="vgg16 = BASELINE configs[4] (the headline); cfg1..cfg4 = the single-layer configs[0..3]; conv = --shape; "
+                         "gemm = the per-position batched GEMM of cfg1 / cfg2 / cfg3b / cfg4 beside torch.bmm (cuBLAS) on the same box")
     ap.add_argument("--shape", default="256,256,56,3", help="--workload conv: C,K,HW,kernel (stride 1, 'same' padding, fp16)")
     ap.add_argument("--batch", type=int, default=0, help="global batch (default: what the configuration names: 256 for vgg16)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
@@ -86,6 +87,8 @@ def parse_args():
     ap.add_argument("--algo", default="auto", choices=["auto", "row", "fused", "staged"],
                     help="fused: one tcgen05 kernel per layer, F(2x2,3x3); staged: three kernels per pass, F(4x4,3x3)")
     ap.add_argument("--product", default="f32", choices=["f32", "f16"], help="dtype of the staged algorithm's products M")
+    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tcgen05", "tf32", "tf32x3"],
+                    help="GEMM engine of the staged algorithm (single-layer workloads)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the cpu_baseline sample")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
@@ -346,7 +349,9 @@ def describe_algorithms(layers):
             d = text[a]
         else:
             m = max(int(v) for v in c.info.tile_m)
-            eng = "tcgen05 GEMM" if int(c.info.gemm_engine) == capi.GEMM_TCGEN05 else "fp32 FMA GEMM"
+            eng = {capi.GEMM_TCGEN05: "tcgen05 GEMM", capi.GEMM_TF32: "tcgen05 tf32 GEMM",
+                   capi.GEMM_TF32X3: "tcgen05 GEMM, three tf32 products of a hi / lo split per multiply"}.get(
+                       int(c.info.gemm_engine), "fp32 FMA GEMM")
             d = (f"F({m}x{m},3x3)" if int(c.info.n_pieces) == 1 and c.ndim == 2 else f"DWM pieces of F({m},r)") + \
                 f" staged: input transform, {eng}, output transform; products fp32"
         if d not in out:
@@ -401,7 +406,59 @@ def layer_errors(args, layers, x_host, dev):
             "tolerance_E_B": 1e-3 if x_host.dtype == torch.float32 else 2e-2, "layers": rows}
 
 
+def run_gemm_compare(args):
+    """winoconv_gemm_batched beside torch.bmm (the library GEMM the reference calls through cublas{S,H}gemmBatched,
+    src/base_conv_launchers.cu:362-367) on the [positions, tiles, C] x [positions, C, K] shapes of the staged path.
+    A side measurement: one JSON line, no contract keys."""
+    import torch
+    from pytorch_winoconv_b200 import capi, engine
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    capi.check(capi.lib().winoconv_device_check(), "winoconv_device_check")
+    shapes = [("cfg1 F(2x2,3x3) fp32", 16, 6272, 64, 64, torch.float32),
+              ("cfg2 F(4x4,3x3) fp16", 36, 1568, 256, 256, torch.float16),
+              ("cfg3b 5x5 pieces fp16", 49, 25088, 128, 128, torch.float16),
+              ("cfg4 F(2,3)^3 fp16", 64, 50176, 64, 64, torch.float16)]
+    rows = []
+    for name, pos, tiles, c, k, dt in shapes:
+        g = torch.Generator().manual_seed(0)
+        v = torch.randn(pos, tiles, c, generator=g).to(dt).to(dev)
+        u = (torch.randn(pos, k, c, generator=g) / c ** 0.5).to(dt).to(dev)
+        m = torch.empty(pos, tiles, k, dtype=torch.float32, device=dev)
+        ut = u.transpose(1, 2).contiguous()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        engines = ([("fp32 fma", capi.GEMM_SIMT), ("tf32", capi.GEMM_TF32), ("tf32 x3", capi.GEMM_TF32X3)]
+                   if dt == torch.float32 else [("tcgen05 f16", capi.GEMM_TCGEN05)])
+        calls = [(n, (lambda e=e: capi.gemm_batched(engine.dtype_code(dt), capi.F32, e, pos, tiles, c, k, v.data_ptr(),
+                                                    u.data_ptr(), m.data_ptr(), stream))) for n, e in engines]
+        calls.append(("torch.bmm (cuBLAS), out in the input dtype", lambda: torch.bmm(v, ut)))
+        if dt == torch.float32:
+            def bmm_tf32():
+                torch.backends.cuda.matmul.allow_tf32 = True
+                torch.bmm(v, ut)
+                torch.backends.cuda.matmul.allow_tf32 = False
+            calls.append(("torch.bmm (cuBLAS), tf32 allowed", bmm_tf32))
+        flops = 2.0 * pos * tiles * c * k
+        res = {}
+        for n, fn in calls:
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            us = 1e3 * e0.elapsed_time(e1) / args.steps
+            res[n] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1)}
+        rows.append({"shape": name, "positions": pos, "tiles": tiles, "c": c, "k": k, "engines": res})
+    print(json.dumps({"workload": "gemm", "steps": args.steps, "note": "eager launches, CUDA events; m in fp32 for the engine", "rows": rows}), flush=True)
+
+
 def run_ours(args):
+    if args.workload == "gemm":
+        return run_gemm_compare(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 and world == 1:
         relaunch_under_torchrun(args)
@@ -481,6 +538,8 @@ def run_ours(args):
             algo_code = {"row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
         conv = engine.WinoConv((batch,) + tuple(sp) + (cc,), w, stride=stride, padding=pad,
                                tile_m=2 if (fused or tm == 2) else 4, algo=algo_code,
+                               gemm_engine={"auto": capi.GEMM_AUTO, "simt": capi.GEMM_SIMT, "tcgen05": capi.GEMM_TCGEN05,
+                                            "tf32": capi.GEMM_TF32, "tf32x3": capi.GEMM_TF32X3}[args.engine],
                                product_dtype=torch.float16 if (args.product == "f16" and not fused and dt == torch.float16) else None)
         out_buf = torch.empty(conv.out_shape, dtype=dt, device=dev)
 
@@ -636,7 +695,19 @@ def run_ours(args):
     # a kernel timed alone is held against the burst figure, one inside a long step against the sustained one;
     # fp32 layers run their products as fp32 FMA: nominal 75 TFLOP/s
     tc_peak_16 = peaks["bf16_tflops"] if single_layer else peaks["bf16_tflops_sustained"]
-    mma_peak = 75.0 if io_dtype == torch.float32 else tc_peak_16
+
+    def product_peak(conv):
+        """TFLOP/s the layer's multiply-adds can be held against: the 16-bit tensor peak; for fp32 inputs half of it
+        per tf32 product (a third of that when every multiply-add is three products of a hi / lo split), or the
+        nominal 75 TFLOP/s of fp32 FMA for the FMA kernel."""
+        if io_dtype != torch.float32:
+            return tc_peak_16, "tensor"
+        eng = int(conv.info.gemm_engine)
+        if eng == capi.GEMM_TF32:
+            return tc_peak_16 / 2, "tensor (tf32)"
+        if eng == capi.GEMM_TF32X3:
+            return tc_peak_16 / 6, "tensor (3 x tf32)"
+        return 75.0, "fp32-fma"
     h = x_dev
     for li, conv in enumerate(layers):
         acc = [0.0, 0.0, 0.0]
@@ -649,6 +720,7 @@ def run_ours(args):
         info = conv.info
         cinfo, cname = contract_info(conv)
         t_ms = sum(st)
+        mma_peak, mma_bound = product_peak(conv)
         t_tc = info.gemm_flops / (mma_peak * 1e12) * 1e3
         t_hbm = info.algorithmic_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
         t_tc_c = cinfo.gemm_flops / (mma_peak * 1e12) * 1e3
@@ -657,7 +729,7 @@ def run_ours(args):
                           "launches": n_launch, "algo": ALGO_NAMES[int(info.algo)],
                           "eff_tflops": round(info.direct_flops / (t_ms * 1e-3) / 1e12, 2),
                           "gemm_tflops": round(info.gemm_flops / (st[1] * 1e-3) / 1e12, 2),
-                          "roof_ms": round(max(t_tc, t_hbm), 4), "roof_bound": "tensor" if t_tc >= t_hbm else "hbm",
+                          "roof_ms": round(max(t_tc, t_hbm), 4), "roof_bound": mma_bound if t_tc >= t_hbm else "hbm",
                           "roof_frac": round(max(t_tc, t_hbm) / t_ms, 4),
                           "contract": cname, "roof_ms_contract": round(max(t_tc_c, t_hbm), 5),
                           "roof_bound_contract": "tensor" if t_tc_c >= t_hbm else "hbm",
@@ -676,7 +748,9 @@ def run_ours(args):
         alg = sum(c.info.gemm_flops for c in layers)
         achieved = alg / (stage_tot[1] * 1e-3) / 1e12
         if io_dtype == torch.float32:
-            peak, unit, bound, kernel = 75.0, "TFLOP/s", "fp32-fma", "gemm_simt_kernel"
+            peak, bound = product_peak(layers[0])
+            unit = "TFLOP/s"
+            kernel = "gemm_simt_kernel" if bound == "fp32-fma" else "gemm_tf32_kernel"
         else:
             peak, unit, bound = tc_peak_16, "TFLOP/s", "tensor"
             kernel = "rowfused_kernel" if is_row else ("fused23_kernel" if is_fused else "gemm_tcgen05_kernel")

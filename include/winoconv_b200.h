@@ -47,9 +47,12 @@ typedef enum winoconv_status {
 typedef enum winoconv_dtype { WINOCONV_F32 = 0, WINOCONV_F16 = 1, WINOCONV_BF16 = 2 } winoconv_dtype_t;
 typedef enum winoconv_wlayout { WINOCONV_W_KCRS = 0, WINOCONV_W_RSCK = 1 } winoconv_wlayout_t;
 typedef enum winoconv_gemm {
-  WINOCONV_GEMM_AUTO = 0,    /* tcgen05 for f16/bf16 inputs, SIMT fp32 FMA for f32 inputs */
+  WINOCONV_GEMM_AUTO = 0,    /* tcgen05 for f16/bf16 inputs, TF32X3 for f32 inputs        */
   WINOCONV_GEMM_SIMT = 1,    /* fp32-accumulate FMA kernel (any dtype; the f32 path)      */
-  WINOCONV_GEMM_TCGEN05 = 2  /* tcgen05.mma + TMEM + TMA (f16 / bf16 inputs only)         */
+  WINOCONV_GEMM_TCGEN05 = 2, /* tcgen05.mma + TMEM + TMA (f16 / bf16 inputs only)         */
+  WINOCONV_GEMM_TF32 = 3,    /* f32 inputs, tcgen05 kind::tf32: 10-bit operand mantissas   */
+  WINOCONV_GEMM_TF32X3 = 4   /* f32 inputs, three tf32 products of a hi / lo operand split */
+                             /* made in shared memory: fp32-class accuracy on tensor cores */
 } winoconv_gemm_t;
 
 typedef enum winoconv_algo {

@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libwinoconv_b200.so")
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_NO_DEVICE = range(7)
 F32, F16, BF16 = 0, 1, 2
 W_KCRS, W_RSCK = 0, 1
-GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
+GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05, GEMM_TF32, GEMM_TF32X3 = 0, 1, 2, 3, 4
 EPI_BIAS, EPI_RELU, EPI_POOL2 = 1, 2, 4
 ALGO_AUTO, ALGO_STAGED, ALGO_FUSED, ALGO_ROW = 0, 1, 2, 3
 MAX_PIECES = 64

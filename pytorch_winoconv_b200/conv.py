@@ -238,7 +238,7 @@ class Conv2d(_WinoConvMixin, nn.Conv2d):
     """``torch.nn.Conv2d`` whose forward is the Winograd / DWM engine (reference: ``conv.py:305-340``).
 
     Extra keyword arguments: ``compute_dtype`` (default ``torch.float16`` as upstream, ``None`` keeps the
-    input's dtype; fp32 runs the fp32-accumulate SIMT path), ``activation`` (``None`` / ``"relu"``),
+    input's dtype; fp32 runs its products as three tf32 tensor-core products of a hi / lo split), ``activation`` (``None`` / ``"relu"``),
     ``pool`` (``None`` / ``2``), ``tile_m`` (0 auto, 2, 4) and ``algo`` (``capi.ALGO_*``).
     """
 

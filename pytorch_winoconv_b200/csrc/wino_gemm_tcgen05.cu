@@ -284,6 +284,206 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   }
 }
 
+// ---- fp32 operands on the tensor cores: kind::tf32, plain or as three products of a hi / lo split -----------------
+// A tf32 multiply keeps 10 mantissa bits of each operand, which is not enough for the 1e-3 bound of the fp32 path
+// (measured: see the cfg1 parity test).  Writing every operand as hi + lo, with hi the value rounded to tf32 and
+// lo = x - hi (exact in fp32), the three products hi*hi + lo*hi + hi*lo leave an error of order 2^-21.  The split
+// is made in shared memory: the epilogue warps, idle during the main loop, rewrite each stage in place as it lands
+// (hi over the loaded values, lo into a second copy at the same offsets, so the 128-byte swizzle carries over) and
+// then hand it to the MMA thread.  V, U and the transforms that produce them are untouched: no second pass over HBM.
+constexpr int BK32 = 32;     // fp32 elements per 128-byte swizzle row
+constexpr int UMMA_K32 = 8;  // reduction depth of one kind::tf32 MMA (32 bytes)
+
+template <int BN, bool SPLIT> struct Cfg32 {
+  static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = (SPLIT ? 2 : 1) * (A_BYTES + B_BYTES);   // [A hi | B hi | A lo | B lo]
+  static constexpr int STAGES = (BN == 256 ? 2 : (BN == 128 ? 3 : 4));
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = RING_BYTES + 1024 + 256;
+  static_assert(RING_BYTES >= 4 * 32 * 36 * 4, "epilogue staging must fit in the ring");
+  static_assert(SMEM_BYTES <= 227 * 1024, "stage ring exceeds shared memory");
+};
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+template <int BN, bool SPLIT>
+__global__ void __launch_bounds__(192, 1) gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_v,
+                                                            const __grid_constant__ CUtensorMap map_u,
+                                                            float *__restrict__ m, int tiles, int c_pad, int k_out,
+                                                            int n_blocks, uint32_t idesc, int n_stages) {
+  using C = Cfg32<BN, SPLIT>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t ring = (raw + 1023u) & ~1023u;
+  uint8_t *ring_ptr = smem_raw + (ring - raw);
+  // The ring holds n_stages stages, no more than the reduction has slabs: a short reduction then leaves room for
+  // several CTAs per SM, whose load, split, MMA and store phases overlap each other.
+  const int ring_bytes = n_stages * C::STAGE_BYTES;
+  const uint32_t bars = ring + ring_bytes;    // full[n_stages], empty[n_stages], split[n_stages], acc_full
+  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(ring_ptr + ring_bytes + 128);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ring_ptr + ring_bytes + 132);
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (n_stages + s); };
+  auto split_bar = [&](int s) { return bars + 8u * (2 * n_stages + s); };
+  const uint32_t acc_bar = bars + 8u * (3 * n_stages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_blk = blockIdx.x % n_blocks, m_blk = blockIdx.x / n_blocks, pos = blockIdx.y;
+  const int n_kb = (c_pad + BK32 - 1) / BK32;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(split_bar(s), 4);          // one arrival per splitting warp
+    }
+    mbar_init(acc_bar, 1);
+    *abort_word = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+  constexpr int HALF_BYTES = C::A_BYTES + C::B_BYTES;     // the loaded (hi) half of a stage
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < n_kb; ++kb) {
+        const int s = kb % n_stages;
+        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) break;
+        mbar_expect_tx(full_bar(s), (uint32_t)HALF_BYTES);
+        const uint32_t a_dst = ring + s * C::STAGE_BYTES;
+        tma_load_3d(a_dst, &map_v, full_bar(s), kb * BK32, m_blk * BM, pos);
+        tma_load_3d(a_dst + C::A_BYTES, &map_u, full_bar(s), kb * BK32, n_blk * BN, pos);
+        issued = kb + 1;
+      }
+      if (*abort_word != 0u) {   // let every load issued land before the CTA exits
+        for (int kb = (issued > n_stages ? issued - n_stages : 0); kb < issued; ++kb) {
+          const long long start = clock64();
+          while (!mbar_try_wait(full_bar(kb % n_stages), (uint32_t)(kb / n_stages) & 1u)) {
+            if (clock64() - start > WAIT_LIMIT_CLOCKS) { atomicCAS(&g_device_error, 0u, (unsigned)ERR_DRAIN); break; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < n_kb && ok; ++kb) {
+        const int s = kb % n_stages;
+        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
+        ok = mbar_wait(SPLIT ? split_bar(s) : full_bar(s), ph, abort_word, ERR_MMA_FULL);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_base = ring + s * C::STAGE_BYTES;
+        const uint64_t a_hi = make_smem_desc(a_base), b_hi = make_smem_desc(a_base + C::A_BYTES);
+        const uint64_t a_lo = make_smem_desc(a_base + HALF_BYTES), b_lo = make_smem_desc(a_base + HALF_BYTES + C::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK32 / UMMA_K32; ++k) {   // 8 fp32 along the reduction = 32 bytes = 2 descriptor address units
+          if (SPLIT) {
+            umma_tf32(tmem_acc, a_lo + 2u * k, b_hi + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_tf32(tmem_acc, a_hi + 2u * k, b_lo + 2u * k, idesc, 1u);
+            umma_tf32(tmem_acc, a_hi + 2u * k, b_hi + 2u * k, idesc, 1u);
+          } else {
+            umma_tf32(tmem_acc, a_hi + 2u * k, b_hi + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(empty_bar(s));
+      }
+      umma_commit(acc_bar);
+    }
+  } else if (SPLIT) {
+    // warps 2..5: rewrite each landed stage as hi (in place) and lo (second half of the stage)
+    const int st = threadIdx.x - 64;      // 0..127
+    bool ok = true;
+    for (int kb = 0; kb < n_kb && ok; ++kb) {
+      const int s = kb % n_stages;
+      const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
+      unsigned got = 0;
+      if (lane == 0) got = mbar_wait(full_bar(s), ph, abort_word, ERR_MMA_FULL) ? 1u : 0u;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got == 0u) { ok = false; break; }
+      float4 *hi = reinterpret_cast<float4 *>(ring_ptr + s * C::STAGE_BYTES);
+      float4 *lo = reinterpret_cast<float4 *>(ring_ptr + s * C::STAGE_BYTES + HALF_BYTES);
+#pragma unroll 4
+      for (int i = st; i < HALF_BYTES / 16; i += 128) {
+        const float4 x = hi[i];
+        float4 h, l;
+        h.x = tf32_round(x.x); h.y = tf32_round(x.y); h.z = tf32_round(x.z); h.w = tf32_round(x.w);
+        l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
+        hi[i] = h;
+        lo[i] = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these stores before the MMA's reads
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(split_bar(s)) : "memory");
+    }
+  }
+  __syncwarp();
+
+  if (warp >= 2) {
+    const int q = warp & 3;
+    unsigned got = 0;
+    if (lane == 0) got = mbar_wait(acc_bar, 0u, abort_word, ERR_EPI_ACC) ? 1u : 0u;
+    got = __shfl_sync(0xffffffffu, got, 0);
+    const bool healthy = got != 0u && *abort_word == 0u;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float *stage = reinterpret_cast<float *>(ring_ptr) + (warp - 2) * (32 * 36);
+    const long long row0 = (long long)m_blk * BM + q * 32;
+    const int rows_valid = (int)max(0LL, min(32LL, (long long)tiles - row0));
+    float *m_rows = m + ((long long)pos * tiles + row0) * k_out + (long long)n_blk * BN;
+    const bool vec_ok = (k_out % 8) == 0;
+    if (healthy) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int cols_valid = min(32, k_out - (n_blk * BN + c0));
+        if (cols_valid <= 0) break;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4 *>(stage + lane * 36 + 4 * j) =
+              make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                          __uint_as_float(r[4 * j + 3]));
+        __syncwarp();
+        if (vec_ok) {
+#pragma unroll
+          for (int it = 0; it < 32 / StoreRow<float>::ROWS_PER_ITER; ++it)
+            StoreRow<float>::run(stage, lane, it, m_rows + c0, (long long)k_out, rows_valid, cols_valid);
+        } else {
+          for (int rr = 0; rr < rows_valid; ++rr)
+            if (lane < cols_valid) m_rows[(long long)rr * k_out + c0 + lane] = stage[rr * 36 + lane];
+        }
+        __syncwarp();
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -308,11 +508,13 @@ static bool make_operand_map(CUtensorMap *map, int dtype, const void *base, int 
                              int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return false;
+  const cuuint64_t esz = dtype == WINOCONV_F32 ? 4ull : 2ull;
   const cuuint64_t dims[3] = {(cuuint64_t)c_pad, (cuuint64_t)rows, (cuuint64_t)positions};
-  const cuuint64_t strides[2] = {(cuuint64_t)c_pad * 2ull, (cuuint64_t)c_pad * 2ull * (cuuint64_t)rows};
-  const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1u};
+  const cuuint64_t strides[2] = {(cuuint64_t)c_pad * esz, (cuuint64_t)c_pad * esz * (cuuint64_t)rows};
+  const cuuint32_t box[3] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows, 1u};   // one 128-byte swizzle row
   const cuuint32_t estr[3] = {1u, 1u, 1u};
-  const CUtensorMapDataType dt = dtype == WINOCONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = dtype == WINOCONV_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == WINOCONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   return enc(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -349,7 +551,48 @@ static cudaError_t pick_bn(int dtype, int positions, long long tiles, int c_pad,
   return run<256, TM>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
 }
 
+template <int BN, bool SPLIT>
+static cudaError_t run32(int positions, long long tiles, int c_pad, int k_out, const void *v, const void *u, void *m,
+                         cudaStream_t s, const char **detail) {
+  using C = Cfg32<BN, SPLIT>;
+  CUtensorMap map_v, map_u;
+  if (!make_operand_map(&map_v, WINOCONV_F32, v, c_pad, tiles, positions, BM) ||
+      !make_operand_map(&map_u, WINOCONV_F32, u, c_pad, k_out, positions, BN)) {
+    *detail = "cuTensorMapEncodeTiled failed (operands must be 16-byte aligned, c_pad a multiple of 8)";
+    return cudaErrorInvalidValue;
+  }
+  auto kern = gemm_tf32_kernel<BN, SPLIT>;
+  const int n_kb = (c_pad + BK32 - 1) / BK32;
+  int n_stages = n_kb < C::STAGES ? n_kb : C::STAGES;
+  if (n_stages * C::STAGE_BYTES < 4 * 32 * 36 * 4) n_stages = C::STAGES;   // the epilogue stages its rows in the ring
+  const int smem_bytes = n_stages * C::STAGE_BYTES + 1024 + 256;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
+  const int n_blocks = (k_out + BN - 1) / BN;
+  const long long m_blocks = (tiles + BM - 1) / BM;
+  if (m_blocks * n_blocks > 0x7fffffffLL) { *detail = "too many tile blocks for one launch"; return cudaErrorInvalidConfiguration; }
+  // instruction descriptor: D = f32, A = B = tf32 (2), both reduction-major, N >> 3, M >> 4
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  dim3 grid((unsigned)(m_blocks * n_blocks), (unsigned)positions), block(192);
+  kern<<<grid, block, smem_bytes, s>>>(map_v, map_u, (float *)m, (int)tiles, c_pad, k_out, n_blocks, idesc, n_stages);
+  return cudaGetLastError();
+}
+
 }  // namespace tc
+
+cudaError_t launch_gemm_tf32(int split, int positions, long long tiles, int c_pad, int k_out, const void *v,
+                             const void *u, void *m, cudaStream_t s, const char **detail) {
+  *detail = "";
+  if (positions <= 0 || tiles <= 0) return cudaSuccess;
+  if (c_pad % 8 != 0 || positions > 65535 || tiles > 0x7fffffffLL) { *detail = "c_pad must be a multiple of 8; positions <= 65535"; return cudaErrorInvalidValue; }
+  if (split) {   // the split stages are twice as large: 128 output channels per CTA at most
+    if (k_out <= 64) return tc::run32<64, true>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
+    return tc::run32<128, true>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  }
+  if (k_out <= 64) return tc::run32<64, false>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  if (k_out <= 128) return tc::run32<128, false>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  return tc::run32<256, false>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
+}
 
 cudaError_t read_and_clear_device_error(cudaStream_t s, unsigned int *code) {
   unsigned int host = 0, zero = 0;

@@ -25,6 +25,11 @@ cudaError_t launch_gemm_simt(int dtype, int product_dtype, int positions, long l
 cudaError_t launch_gemm_tcgen05(int dtype, int product_dtype, int positions, long long tiles, int c_pad, int k_out,
                                 const void *v, const void *u, void *m, cudaStream_t s, const char **detail);
 
+// fp32 operands on the tensor cores (kind::tf32): split = 0 plain tf32 products, split = 1 three products of a
+// hi / lo split made in shared memory (fp32-class accuracy).  m in fp32.
+cudaError_t launch_gemm_tf32(int split, int positions, long long tiles, int c_pad, int k_out, const void *v,
+                             const void *u, void *m, cudaStream_t s, const char **detail);
+
 // Fused F(2x2,3x3) path (f16 / bf16): transformed filter u [16][K][R], then one kernel for the whole layer.
 cudaError_t launch_fused_filter_transform(const FGeom &g, int dtype, const void *w, void *u, cudaStream_t s);
 cudaError_t launch_fused_forward(const FGeom &g, int dtype, const void *x, const void *u, const void *bias, void *y,

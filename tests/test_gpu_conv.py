@@ -196,6 +196,26 @@ def test_cfg1_fp32_f23():
     print("cfg1 engine", err, "reference algebra (CPU fp32)", ref)
 
 
+def test_cfg1_fp32_product_arithmetic_table():
+    """configs[0] with the three ways of forming the fp32 products: fp32 FMA, one tf32 product, three tf32 products of
+    a hi / lo split.  The 1e-3 bound of the fp32 path holds for the first and the last; the measured E_B of each is
+    printed (and quoted in the design notes)."""
+    x = seeded((8, 64, 56, 56), 0)
+    w = wo.kaiming_normal((64, 64, 3, 3), 1)
+    o = wo.direct_conv_f64(x, w, padding=1)
+    table = {}
+    for name, eng in (("fp32 fma", capi.GEMM_SIMT), ("tf32", capi.GEMM_TF32), ("tf32 x3", capi.GEMM_TF32X3)):
+        for tm in (2, 4):
+            y, conv = run_engine(x, w, padding=1, tile_m=tm, gemm_engine=eng)
+            assert conv.info.gemm_engine == eng
+            table[(name, tm)] = wo.error_metrics(y, o)["E_B"]
+    print("cfg1 E_B by product arithmetic and tile:", {f"{k[0]} F({k[1]}x{k[1]},3x3)": "%.3g" % v for k, v in table.items()})
+    for tm in (2, 4):
+        assert table[("fp32 fma", tm)] <= 1e-3 and table[("tf32 x3", tm)] <= 1e-3
+        assert table[("tf32 x3", tm)] <= 4 * table[("fp32 fma", tm)] + 1e-6
+        assert table[("tf32", tm)] <= 2e-2          # bounded, but (measured) over the fp32 tolerance
+
+
 @pytest.mark.parametrize("product_dtype", [None, torch.float16])
 @pytest.mark.parametrize("seed", [0, 17])
 def test_cfg2_fp16_f43(product_dtype, seed):

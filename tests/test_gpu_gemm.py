@@ -31,7 +31,7 @@ def _operands(pos, tiles, c_pad, k_out, dtype, seed=0):
     return v, u
 
 
-def _run(engine_code, dtype, pdtype, pos, tiles, c_pad, k_out):
+def _run(engine_code, dtype, pdtype, pos, tiles, c_pad, k_out, tol_override=None):
     v, u = _operands(pos, tiles, c_pad, k_out, dtype)
     ref = torch.matmul(v.double(), u.double().transpose(1, 2))
     vd, ud = v.cuda(), u.cuda()
@@ -47,7 +47,28 @@ def _run(engine_code, dtype, pdtype, pos, tiles, c_pad, k_out):
     tol = {torch.float32: 2e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[pdtype]
     if dtype != torch.float32 and pdtype == torch.float32:
         tol = 2e-5     # exact products of rounded inputs, fp32 accumulation
+    if tol_override is not None:
+        tol = tol_override
     assert err <= tol, (err, tol)
+    return err
+
+
+@pytest.mark.parametrize("pos,tiles,c_pad,k_out", CASES)
+def test_tf32x3_gemm_holds_the_fp32_tolerance(pos, tiles, c_pad, k_out):
+    """fp32 operands on the tensor cores as three tf32 products of a hi / lo split: the same 2e-5 as the FMA kernel."""
+    _run(capi.GEMM_TF32X3, torch.float32, torch.float32, pos, tiles, c_pad, k_out)
+
+
+@pytest.mark.parametrize("pos,tiles,c_pad,k_out", CASES)
+def test_plain_tf32_gemm(pos, tiles, c_pad, k_out):
+    """one tf32 product per multiply: operands keep 10 mantissa bits, so the bound is 2^-10-class, not fp32-class"""
+    _run(capi.GEMM_TF32, torch.float32, torch.float32, pos, tiles, c_pad, k_out, tol_override=3e-3)
+
+
+def test_tf32_engines_refuse_16bit_operands():
+    with pytest.raises(capi.WinoconvError) as ei:
+        capi.gemm_batched(capi.F16, capi.F32, capi.GEMM_TF32X3, 1, 128, 64, 64, 256, 256, 256)
+    assert ei.value.status == capi.ERR_UNSUPPORTED
 
 
 @pytest.mark.parametrize("pos,tiles,c_pad,k_out", CASES)
