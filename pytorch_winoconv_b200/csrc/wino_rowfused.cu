@@ -173,14 +173,52 @@ __device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
                : "r"(taddr));
 }
 
+// two fp32 values in one 64-bit register, and the packed adds of sm_100 on them
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t sub_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <typename T> struct P2;
 template <> struct P2<__half> {
   using V = __half2;
   static __device__ __forceinline__ V from(float a, float b) { return __floats2half2_rn(a, b); }
+  // (lo, hi) fp32 pair -> packed 16-bit pair, lo in the low half
+  static __device__ __forceinline__ uint32_t round_pair(uint64_t v) {
+    uint32_t r;
+    asm("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.f16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(v));
+    return r;
+  }
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+  }
 };
 template <> struct P2<__nv_bfloat16> {
   using V = __nv_bfloat162;
   static __device__ __forceinline__ V from(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  static __device__ __forceinline__ uint32_t round_pair(uint64_t v) {
+    uint32_t r;
+    asm("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(v));
+    return r;
+  }
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+  }
 };
 template <typename T> struct __align__(16) V8 { typename P2<T>::V h[4]; };
 template <typename T> __device__ __forceinline__ V8<T> v8_add(const V8<T> &a, const V8<T> &b) {
@@ -663,38 +701,39 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
               if (lane == 0) { if (PAIR) mbar_arrive_rank0(acc_empty(ab)); else mbar_arrive(acc_empty(ab)); }
             }
             const int kbase = k0 + cc;
-            float y0[8], y1[8];
+            // A^T along W on channel pairs with the packed fp32 adds of sm_100 (y0 = a0 + a1 + a2, y1 = a1 - a2 - a3), one
+            // rounding to the 16-bit pair, then ReLU and the pool's maxima on the packed halves: rounding is monotonic,
+            // so max-then-round and round-then-max give the same bits at half the instructions.
+            uint32_t v0[4], v1[4];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const float a0 = __uint_as_float(p0[c]), a1 = __uint_as_float(p1[c]), a2 = __uint_as_float(p2[c]), a3 = __uint_as_float(p3[c]);
-              y0[c] = a0 + a1 + a2;
-              y1[c] = a1 - a2 - a3;
-            }
-            if (has_bias) {
-#pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                const float bv = (kbase + c < K) ? Elem<T>::load(bias + kbase + c) : 0.f;
-                y0[c] += bv;
-                y1[c] += bv;
+            for (int c = 0; c < 4; ++c) {
+              const uint64_t a0 = pack_f32x2(p0[2 * c], p0[2 * c + 1]), a1 = pack_f32x2(p1[2 * c], p1[2 * c + 1]);
+              const uint64_t a2 = pack_f32x2(p2[2 * c], p2[2 * c + 1]), a3 = pack_f32x2(p3[2 * c], p3[2 * c + 1]);
+              uint64_t y0 = add_f32x2(add_f32x2(a0, a1), a2);
+              uint64_t y1 = sub_f32x2(sub_f32x2(a1, a2), a3);
+              if (has_bias) {
+                const float b_lo = (kbase + 2 * c < K) ? Elem<T>::load(bias + kbase + 2 * c) : 0.f;
+                const float b_hi = (kbase + 2 * c + 1 < K) ? Elem<T>::load(bias + kbase + 2 * c + 1) : 0.f;
+                const uint64_t bv = pack_f32x2(__float_as_uint(b_lo), __float_as_uint(b_hi));
+                y0 = add_f32x2(y0, bv);
+                y1 = add_f32x2(y1, bv);
               }
+              v0[c] = P2<T>::round_pair(y0);
+              v1[c] = P2<T>::round_pair(y1);
             }
             if (pool) {
 #pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                float mx = fmaxf(y0[c], y1[c]);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, g.CBW));   // the other output row of the 2x2 window
-                y0[c] = relu ? fmaxf(mx, 0.f) : mx;
+              for (int c = 0; c < 4; ++c) {
+                uint32_t mx = P2<T>::max2(v0[c], v1[c]);
+                mx = P2<T>::max2(mx, __shfl_xor_sync(0xffffffffu, mx, g.CBW));   // the other output row of the 2x2 window
+                v0[c] = relu ? P2<T>::max2(mx, 0u) : mx;
               }
             } else if (relu) {
 #pragma unroll
-              for (int c = 0; c < 8; ++c) { y0[c] = fmaxf(y0[c], 0.f); y1[c] = fmaxf(y1[c], 0.f); }
+              for (int c = 0; c < 4; ++c) { v0[c] = P2<T>::max2(v0[c], 0u); v1[c] = P2<T>::max2(v1[c], 0u); }
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const typename P2<T>::V v0 = P2<T>::from(y0[2 * c], y0[2 * c + 1]), v1 = P2<T>::from(y1[2 * c], y1[2 * c + 1]);
-              pk0[4 * h + c] = *reinterpret_cast<const uint32_t *>(&v0);
-              pk1[4 * h + c] = *reinterpret_cast<const uint32_t *>(&v1);
-            }
+            for (int c = 0; c < 4; ++c) { pk0[4 * h + c] = v0[c]; pk1[4 * h + c] = v1[c]; }
           }
           const int kb16 = k0 + c0;
           if (kb16 < K) {
