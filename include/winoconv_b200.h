@@ -5,7 +5,9 @@
  * exits.  Every entry point returns a winoconv_status_t; winoconv_last_error() gives the
  * detail text of the calling thread's last failure.  All device memory is owned by the
  * caller.  No entry point allocates or frees device memory and none synchronises the device;
- * work is enqueued on the stream passed in (NULL = the legacy default stream).
+ * work is enqueued on the stream passed in (NULL = the legacy default stream).  The library keeps
+ * per-device state (kernel attributes, the address of its built-in scratch array) for the life of
+ * the process: do not call cudaDeviceReset while it is in use.
  *
  * Data layout (all contiguous, channels last, as the reference's native op takes them):
  *   activations  x [N, D, H, W, C]     (D = 1 for 2-D convolutions)

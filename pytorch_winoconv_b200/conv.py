@@ -46,6 +46,7 @@ class _WinoConvMixin:
     """Shared forward of :class:`Conv2d` and :class:`Conv3d` (``self`` is a ``torch.nn._ConvNd``)."""
 
     _nd: int = 2
+    MAX_CACHED_PLANS = 8      # distinct input shapes (and backward shapes) kept per module; the oldest is dropped
 
     def _init_wino(self, compute_dtype, activation, pool, tile_m, algo):
         if activation not in (None, "relu"):
@@ -63,7 +64,7 @@ class _WinoConvMixin:
         self.pool = 2 if pool == 2 else None
         self.tile_m = int(tile_m)
         self.algo = int(algo)
-        self._plans = {}          # (input shape, dtype, device) -> engine.WinoConv
+        self._plans = {}          # input shape (or backward key) -> engine.WinoConv, most recently used last
         self._weight_key = None   # identity of the weight the cached plans were built from
 
     # -- cache -------------------------------------------------------------------------------------
@@ -76,7 +77,9 @@ class _WinoConvMixin:
         if key != self._weight_key:            # the parameters changed: every cached filter transform is stale
             self._plans.clear()
             self._weight_key = key
-        plan = self._plans.get(in_shape_cl)
+        plan = self._plans.pop(in_shape_cl, None)
+        if plan is not None:
+            self._plans[in_shape_cl] = plan            # most recently used last
         if plan is None:
             w = self.weight.detach().to(device=device, dtype=dtype)
             b = None if self.bias is None else self.bias.detach().to(device=device, dtype=dtype)
@@ -84,6 +87,8 @@ class _WinoConvMixin:
                                    padding=tuple(int(p) for p in self.padding), tile_m=self.tile_m, bias=b,
                                    relu=self.activation == "relu", pool2=self.pool == 2, algo=self.algo)
             self._plans[in_shape_cl] = plan
+            while len(self._plans) > self.MAX_CACHED_PLANS:      # each plan holds its own transformed filter
+                self._plans.pop(next(iter(self._plans)))
         return plan
 
     # -- forward -----------------------------------------------------------------------------------
@@ -254,8 +259,8 @@ class Conv2d(_WinoConvMixin, nn.Conv2d):
 
 
 class Conv3d(_WinoConvMixin, nn.Conv3d):
-    """``torch.nn.Conv3d`` on the engine (reference: ``conv.py:446-481``); arguments as :class:`Conv2d`.
-    The 2x2 pool of the epilogue acts on H and W."""
+    """``torch.nn.Conv3d`` on the engine (reference: ``conv.py:446-481``); arguments as :class:`Conv2d`,
+    except ``pool``: the epilogue's 2x2 max-pool is a 2-D operation and is refused here."""
 
     _nd = 3
 
@@ -263,6 +268,8 @@ class Conv3d(_WinoConvMixin, nn.Conv3d):
                  padding_mode="zeros", device=None, dtype=None, *, compute_dtype: Optional[torch.dtype] = torch.float16,
                  activation: Optional[str] = None, pool: Optional[int] = None, tile_m: int = 0,
                  algo: int = capi.ALGO_AUTO):
+        if pool == 2:
+            raise ValueError("pool=2 is the 2-D epilogue max-pool: not available on Conv3d")
         nn.Conv3d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias,
                            padding_mode, device=device, dtype=dtype)
         self._init_wino(compute_dtype, activation, pool, tile_m, algo)

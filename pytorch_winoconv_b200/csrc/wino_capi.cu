@@ -404,7 +404,11 @@ static int forward_impl(const winoconv_desc_t *desc, const void *x, const void *
   if (plan.fused || plan.row) {   // one kernel, no V / M scratch
     if ((st = winoconv_device_check()) != WINOCONV_OK) return st;
     cudaStream_t fs = (cudaStream_t)stream;
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    struct EventPair {   // destroyed on every way out
+      cudaEvent_t a = nullptr, b = nullptr;
+      ~EventPair() { if (a) cudaEventDestroy(a); if (b) cudaEventDestroy(b); }
+    } ev;
+    cudaEvent_t &e0 = ev.a, &e1 = ev.b;
     cudaError_t e = cudaSuccess;
     if (stage_ms) {
       e = cudaEventCreate(&e0);
@@ -422,7 +426,6 @@ static int forward_impl(const winoconv_desc_t *desc, const void *x, const void *
       e = cudaEventRecord(e1, fs);
       if (e == cudaSuccess) e = cudaEventSynchronize(e1);
       if (e == cudaSuccess) e = cudaEventElapsedTime(&stage_ms[1], e0, e1);
-      cudaEventDestroy(e0); cudaEventDestroy(e1);
       if (e != cudaSuccess) return cuda_fail(e, "event timing");
     }
     return WINOCONV_OK;
@@ -497,7 +500,9 @@ int winoconv_forward_timed(const winoconv_desc_t *desc, const void *x, const voi
 
 // ---- scratch that is part of the library image (winoconv_forward_static) ---------------------------------
 // In host code the name below is only a handle for cudaGetSymbolAddress; the address kernels may use is
-// looked up once per device and kept in g_static_scratch_addr.
+// looked up once per device and kept in g_static_scratch_addr.  The cache (like the launch-attribute caches of the
+// kernels) is keyed by device ordinal and assumes the device's primary context lives as long as the process: a
+// program that calls cudaDeviceReset must not use the library afterwards.
 static __device__ __align__(256) unsigned char g_static_scratch[WINOCONV_STATIC_SCRATCH_BYTES];
 static void *g_static_scratch_addr[64] = {};
 static std::mutex g_static_scratch_mu;

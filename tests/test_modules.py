@@ -30,6 +30,8 @@ def test_unsupported_arguments_raise():
         wconv.Conv2d(4, 4, 3, activation="gelu")
     with pytest.raises(ValueError):
         wconv.Conv2d(4, 4, 3, pool=3)
+    with pytest.raises(ValueError):
+        wconv.Conv3d(4, 4, 3, pool=2)          # the epilogue pool is 2-D
 
 
 def test_cpu_input_is_refused_loudly():
