@@ -100,6 +100,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
   asm volatile(
       "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
@@ -281,6 +286,10 @@ struct RGeom {
   int n_nblocks;
   long long n_items;
   unsigned epilogue;
+  // Few-channel input read as it lies (C < 8, e.g. RGB): the TMA map addresses x as [N, D, H, W * C], a patch row
+  // is raw_row_el consecutive elements starting at a multiple of eight, the first patch pixel raw_off elements in.
+  int raw_c;              // 0: the map addresses [N, D, H, W, Cp]; else the caller's channel count
+  int raw_off, raw_row_el;
 };
 
 template <typename T, int BN, int MB, bool PAIR>
@@ -402,8 +411,12 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             if (!mbar_wait_warp(raw_empty(s), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_RAW_EMPTY)) { alive = false; break; }
             if (lane == 0) {
               mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
-              tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
-                          od + kd - g.pD, n);
+              if (g.raw_c)   // rows of W * C elements: start at the multiple of eight at or below the first patch pixel
+                tma_load_4d(base + sl.off_raw[s], &map_x, raw_full(s), (cb * g.CBW * 2 - g.pW) * g.raw_c - g.raw_off,
+                            rb * (MB * g.RB) - g.pH, od + kd - g.pD, n);
+              else
+                tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
+                            od + kd - g.pD, n);
             }
             ++it;
           }
@@ -451,7 +464,18 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           for (int row = ptid >> vshift; row < n_tasks; row += N_PROD >> vshift) {
             const int ir = row >> cbw_shift, cp = row - (ir << cbw_shift);
             V8<T> o0, o1, o2, o3;
-            if (real) {
+            if (real && g.raw_c) {
+              // the caller's few channels, gathered from the raw row into 8-channel vectors (zeros above raw_c)
+              const T *src = reinterpret_cast<const T *>(raw) + (size_t)ir * g.raw_row_el + g.raw_off + (2 * cp + 3 * w) * g.raw_c;
+              __align__(16) T dv[4][8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) dv[i][c] = (c < g.raw_c) ? src[i * g.raw_c + c] : T(0.f);
+              const V8<T> d0 = *reinterpret_cast<const V8<T> *>(dv[0]), d1 = *reinterpret_cast<const V8<T> *>(dv[1]);
+              const V8<T> d2 = *reinterpret_cast<const V8<T> *>(dv[2]), d3 = *reinterpret_cast<const V8<T> *>(dv[3]);
+              o0 = v8_sub<T>(d0, d2); o1 = v8_add<T>(d1, d2); o2 = v8_sub<T>(d2, d1); o3 = v8_sub<T>(d1, d3);
+            } else if (real) {
               const uint8_t *src = raw + ((size_t)(ir * g.patch_w + 2 * cp + 3 * w) * KC + v * 8) * 2;
               V8<T> d0, d1, d2, d3;
               *reinterpret_cast<uint4 *>(&d0) = *reinterpret_cast<const uint4 *>(src);
@@ -932,9 +956,21 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   p.pair = (pair_env != 0 && p.MB == 1 && d.N >= 2) ? 1 : 0;
   p.n_items = (long long)(p.pair ? (d.N + 1) / 2 : d.N) * d.oD * p.n_rb * p.n_cb * p.n_nblocks;
   if (p.patch_w > 256 || p.patch_h > 256) return false;
+  // Fewer than eight channels (RGB): TMA wants 16-byte pixels, but a row of W * C elements is a legal innermost
+  // dimension when W * C is a multiple of eight, and a block's first pixel then always lies the same number of elements
+  // past a multiple of eight (a block is 16 or 32 pixels wide).  The producers gather the few channels into 8-channel
+  // vectors as they transform, so no padded copy of x is made.  WINOCONV_ROW_RAWC=0 keeps the padding pass.
+  static const int rawc_env = [] { const char *v = getenv("WINOCONV_ROW_RAWC"); return v && *v ? atoi(v) : 1; }();
+  p.raw_c = 0; p.raw_off = 0; p.raw_row_el = 0;
+  if (d.phases <= 1 && d.C < 8 && ((long long)d.W * d.C) % 8 == 0 && rawc_env != 0) {
+    const int off = ((-(d.pW * d.C)) % 8 + 8) % 8;
+    const int row_el = (off + p.patch_w * d.C + 7) / 8 * 8;
+    if (row_el <= 256) { p.raw_c = d.C; p.raw_off = off; p.raw_row_el = row_el; }
+  }
   // shared memory: 2 raw patches, 2 slab sets (1 if two do not leave room for 3 filter stages), then as many
   // filter stages as fit (2..8)
-  const int raw_bytes = ((p.patch_h * p.patch_w * KC * 2 + 127) / 128) * 128;
+  const int raw_box_bytes = p.raw_c ? p.patch_h * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;
+  const int raw_bytes = ((raw_box_bytes + 127) / 128) * 128;
   const int a_bytes = ((4 * p.slab_rows * 64 + 1023) / 1024) * 1024;
   const int b_stage = 4 * (p.pair ? p.BN / 2 : p.BN) * 64;
   const int budget = 227 * 1024;
@@ -1035,8 +1071,9 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   g.PW = p.PW; g.RB = p.RB; g.CBW = p.CBW; g.MB = p.MB; g.n_rb = p.n_rb; g.n_cb = p.n_cb; g.slab_rows = p.slab_rows;
   g.patch_h = p.patch_h; g.patch_w = p.patch_w; g.n_chunks = p.n_chunks; g.n_nblocks = p.n_nblocks;
   g.n_items = p.n_items; g.epilogue = d.epilogue;
+  g.raw_c = p.raw_c; g.raw_off = p.raw_off; g.raw_row_el = p.raw_row_el;
   Smem sl;
-  sl.raw_bytes = p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
+  sl.raw_bytes = p.raw_c ? p.patch_h * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
   sl.a_bytes = p.a_bytes; sl.b_stage_bytes = p.b_stage_bytes; sl.n_b_stages = p.n_b_stages;
   sl.n_a_bufs = p.n_a_bufs;
   sl.b_group = p.b_group;
@@ -1097,7 +1134,7 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { *detail = "phase gather launch failed"; return e; }
     xin = pad_ws;
-  } else if (p.Cp != d.C) {   // channels not a multiple of 8: TMA needs 16-byte pixel strides, so pad into scratch first
+  } else if (p.Cp != d.C && !p.raw_c) {   // channels not a multiple of 8: TMA needs 16-byte pixel strides, so pad into scratch first
     if (!pad_ws) { *detail = "channel padding scratch missing"; return cudaErrorInvalidValue; }
     const long long pixels = (long long)d.N * d.D * d.H * d.W;
     const unsigned blocks = (unsigned)((pixels * (p.Cp / 8) + 255) / 256);
@@ -1111,7 +1148,18 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   }
   const CUtensorMapDataType dt = dtype == WINOCONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap mx, mu;
-  {
+  if (p.raw_c) {   // x as it lies: [N, D, H, W * C]
+    const cuuint64_t row = (cuuint64_t)d.W * d.C;
+    const cuuint64_t dims[4] = {row, (cuuint64_t)d.H, (cuuint64_t)d.D, (cuuint64_t)d.N};
+    const cuuint64_t st[3] = {row * 2ull, row * 2ull * d.H, row * 2ull * d.H * d.D};
+    const cuuint32_t box[4] = {(cuuint32_t)p.raw_row_el, (cuuint32_t)p.patch_h, 1u, 1u};
+    const cuuint32_t es[4] = {1u, 1u, 1u, 1u};
+    if (enc(&mx, dt, 4, const_cast<void *>(xin), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      *detail = "cuTensorMapEncodeTiled failed for the few-channel input";
+      return cudaErrorInvalidValue;
+    }
+  } else {
     const cuuint64_t dims[5] = {(cuuint64_t)p.Cp, (cuuint64_t)d.W, (cuuint64_t)d.H, (cuuint64_t)d.D, (cuuint64_t)d.N};
     const cuuint64_t st[4] = {(cuuint64_t)p.Cp * 2ull, (cuuint64_t)p.Cp * 2ull * d.W, (cuuint64_t)p.Cp * 2ull * d.W * d.H,
                               (cuuint64_t)p.Cp * 2ull * d.W * d.H * d.D};

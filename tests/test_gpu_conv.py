@@ -89,6 +89,18 @@ ROW_CASES = [c for c in SMALL + FUSED_EXTRA if c[7] != 4 and c[4][-2] <= 7 * c[5
     (1, 8, 16, (9, 12, 11), (3, 3, 3), 2, 1, 2),   # 3-D stride 2: eight phases
 ]
 
+# fewer than eight channels with W * C a multiple of eight: x is read as it lies (no padded copy), the producers gather
+# the channels; (C, padding) pairs that put the first patch pixel 0, 3, 5 and 6 elements past a multiple of eight
+RAW_FEW_CHANNEL_CASES = [
+    (2, 3, 64, (30, 32), (3, 3), 1, 1, 2),         # RGB, element offset 5
+    (3, 3, 16, (45, 40), (5, 5), 1, 2, 2),         # RGB 5x5: two windows, odd batch, offset 2
+    (1, 2, 8, (20, 24), (3, 3), 1, 0, 2),          # two channels, no padding: offset 0
+    (2, 5, 8, (18, 16), (3, 3), 1, 1, 2),          # five channels: offset 3
+    (1, 6, 8, (16, 20), (7, 7), 1, 3, 2),          # six channels, 7x7: three windows, offset 6, the widest raw row
+    (1, 4, 4, (5, 9, 8), (3, 3, 3), 1, 1, 2),      # 3-D
+]
+ROW_CASES = ROW_CASES + RAW_FEW_CHANNEL_CASES
+
 
 @pytest.mark.parametrize("n,c,k,sp,ks,stride,pad,m", ROW_CASES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -98,6 +110,8 @@ def test_row_piece_cases(n, c, k, sp, ks, stride, pad, m, dtype):
     w = wo.kaiming_normal((k, c) + ks, 12).to(dtype)
     y, conv = run_engine(x, w, stride=stride, padding=pad, tile_m=2, algo=capi.ALGO_ROW)
     assert conv.info.algo == capi.ALGO_ROW and conv.info.positions == 4
+    if (n, c, k, sp, ks, stride, pad, m) in RAW_FEW_CHANNEL_CASES:
+        assert conv.info.input_ws_bytes == 0 and conv.launches_per_call == 1      # no padded copy of x
     check_against_oracle(x, w, y, stride=stride, padding=pad)
 
 

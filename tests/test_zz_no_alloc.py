@@ -53,8 +53,9 @@ def test_static_scratch_forward_matches_on_consecutive_calls():
 
 
 def test_static_scratch_serves_the_single_kernel_paths():
-    # the row kernel's only scratch: channel padding (3 -> 8) and the stride-2 phase gather (4 x 3 -> 16 channels)
-    xa, ca = _layer(3, 4, 3, 32, 40, 3, 1, torch.float16)
+    # the row kernel's only scratch: channel padding (3 -> 8; a row of 41 x 3 elements is not a multiple of eight, so
+    # the input cannot be read as it lies) and the stride-2 phase gather (4 x 3 -> 16 channels)
+    xa, ca = _layer(3, 4, 3, 32, 41, 3, 1, torch.float16)
     xb, cb = _layer(4, 4, 3, 32, 41, 7, 3, torch.float16, stride=2)
     assert ca.info.algo == capi.ALGO_ROW and cb.info.algo == capi.ALGO_ROW
     assert 0 < int(ca.info.input_ws_bytes) <= capi.STATIC_SCRATCH_BYTES
@@ -73,8 +74,9 @@ def test_static_scratch_refuses_oversized_layers():
 
 
 def test_static_scratch_refuses_an_oversized_row_layer_and_names_the_way_out():
-    # 3 -> 64 at 224 x 224, batch 64: the row kernel's 8-channel copy of the input is 51 MB > 32 MiB
-    d = capi.make_desc(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=3, pad=1)
+    # 7x7 stride-2 stem, 3 -> 64 at 224 x 224, batch 96: the phase-gathered copy of the input (115 x 115 x 16 channels
+    # per image) is 41 MB > 32 MiB
+    d = capi.make_desc(ndim=2, batch=96, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3)
     assert capi.plan(d).algo == capi.ALGO_ROW and capi.plan(d).input_ws_bytes > capi.STATIC_SCRATCH_BYTES
     with pytest.raises(capi.WinoconvError) as ei:
         capi.forward_static(d, 256, 256, None, 256)
