@@ -74,9 +74,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4", "conv", "gemm"],
+    ap.add_argument("--workload", default="vgg16", choices=["vgg16", "cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4", "conv", "gemm", "mma-rate"],
                     help="vgg16 = BASELINE configs[4] (the headline); cfg1..cfg4 = the single-layer configs[0..3]; conv = --shape; "
-                         "gemm = the per-position batched GEMM of cfg1 / cfg2 / cfg3b / cfg4 beside torch.bmm (cuBLAS) on the same box")
+                         "gemm = the per-position batched GEMM of cfg1 / cfg2 / cfg3b / cfg4 beside torch.bmm (cuBLAS) on the same box; "
+                         "mma-rate = clocks per tcgen05.mma by accumulator width, issuing threads and operand placement")
     ap.add_argument("--shape", default="256,256,56,3", help="--workload conv: C,K,HW,kernel (stride 1, 'same' padding, fp16)")
     ap.add_argument("--batch", type=int, default=0, help="global batch (default: what the configuration names: 256 for vgg16)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
@@ -456,9 +457,33 @@ def run_gemm_compare(args):
     print(json.dumps({"workload": "gemm", "steps": args.steps, "note": "eager launches, CUDA events; m in fp32 for the engine", "rows": rows}), flush=True)
 
 
+def run_mma_rate(args):
+    """The calibration probe behind the planner's accumulator width: clocks per tcgen05.mma (M = 128 per SM, K = 16)."""
+    import torch
+    from pytorch_winoconv_b200 import capi
+    torch.cuda.set_device(0)
+    rows = []
+    for pair in (False, True):
+        for a_tmem in (False, True):
+            for thr in (1, 2, 4):
+                for n in (16, 32, 64, 128, 256):
+                    try:
+                        total, issue = capi.probe_mma_rate(pair, a_tmem, n, thr, 512)
+                    except capi.WinoconvError as exc:
+                        if exc.status == capi.ERR_UNSUPPORTED:      # the accumulators of that many threads do not fit
+                            continue
+                        raise
+                    rows.append({"cta_pair": pair, "a_operand": "tmem" if a_tmem else "smem", "threads": thr, "n": n,
+                                 "clocks_per_mma": round(total, 1), "issue_clocks_per_mma_one_thread": round(issue, 1),
+                                 "ideal_clocks": n / 2})
+    print(json.dumps({"workload": "mma-rate", "m_rows_per_sm": 128, "k": 16, "rows": rows}), flush=True)
+
+
 def run_ours(args):
     if args.workload == "gemm":
         return run_gemm_compare(args)
+    if args.workload == "mma-rate":
+        return run_mma_rate(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 and world == 1:
         relaunch_under_torchrun(args)

@@ -244,6 +244,18 @@ WINOCONV_API int winoconv_concat(const float *tiles, float *y, int batch, int ou
 WINOCONV_API int winoconv_add(const float *a, const float *b, float *c, int64_t n, void *stream);
 
 /*
+ * Calibration probe: clocks per tcgen05.mma (M = 128 rows per SM, K = 16, f16 operands, fp32 accumulate) for an
+ * accumulator n_cols wide (a multiple of 16, <= 256), issued by n_threads (1, 2 or 4) threads with their own
+ * accumulators, with the A operand in shared memory (a_in_tmem = 0) or tensor memory (1), on one SM or across a
+ * CTA pair (cta_pair = 1: M = 256 over both).  Writes the span from first issue to last completion divided by
+ * the MMAs issued, and (optionally) the issuing cost per MMA seen by one thread.  Synchronises the stream.  The
+ * planner's preference for 128-column accumulators and the design notes' bandwidth figures come from this probe
+ * (`python bench.py --workload mma-rate` prints the table).  No counterpart in the reference.
+ */
+WINOCONV_API int winoconv_probe_mma_rate(int cta_pair, int a_in_tmem, int n_cols, int n_threads, int n_mma,
+                                         float *clocks_per_mma, float *issue_clocks_per_mma, void *stream);
+
+/*
  * Device error word of the tcgen05 GEMM: bounded mbarrier waits store a code here instead of
  * spinning forever.  Reads and clears it (synchronises the stream).  0 = no error.
  */

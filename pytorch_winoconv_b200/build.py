@@ -25,7 +25,7 @@ INCLUDE = os.path.join(ROOT, "include")
 BUILD_DIR = os.path.join(ROOT, "build", "winoconv")
 CAPI_LIB = os.path.join(PKG_DIR, "libwinoconv_b200.so")
 
-CUDA_SOURCES = ["wino_transforms.cu", "wino_gemm_simt.cu", "wino_gemm_tcgen05.cu", "wino_fused23.cu", "wino_rowfused.cu", "wino_capi.cu"]
+CUDA_SOURCES = ["wino_transforms.cu", "wino_gemm_simt.cu", "wino_gemm_tcgen05.cu", "wino_fused23.cu", "wino_rowfused.cu", "wino_probe.cu", "wino_capi.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -27,7 +27,7 @@ EXPORTED_SYMBOLS = (
     "winoconv_abi_version", "winoconv_status_string", "winoconv_last_error", "winoconv_device_check",
     "winoconv_plan", "winoconv_plan_pieces", "winoconv_filter_transform", "winoconv_forward",
     "winoconv_forward_timed", "winoconv_forward_static", "winoconv_gemm_batched", "winoconv_split",
-    "winoconv_concat", "winoconv_add", "winoconv_read_device_error",
+    "winoconv_concat", "winoconv_add", "winoconv_read_device_error", "winoconv_probe_mma_rate",
 )
 
 
@@ -85,6 +85,9 @@ def lib() -> ctypes.CDLL:
     L.winoconv_concat.argtypes = [c_void_p, c_void_p] + [c_int] * 8 + [c_void_p]
     L.winoconv_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     L.winoconv_read_device_error.argtypes = [c_void_p, POINTER(c_uint32)]
+    L.winoconv_probe_mma_rate.argtypes = [c_int, c_int, c_int, c_int, c_int, POINTER(ctypes.c_float),
+                                          POINTER(ctypes.c_float), c_void_p]
+    L.winoconv_probe_mma_rate.restype = c_int
     for name in ("winoconv_plan", "winoconv_plan_pieces", "winoconv_filter_transform", "winoconv_forward",
                  "winoconv_forward_timed", "winoconv_forward_static", "winoconv_gemm_batched", "winoconv_split",
                  "winoconv_concat", "winoconv_add", "winoconv_read_device_error"):
@@ -179,3 +182,11 @@ def read_device_error(stream: int = 0) -> int:
     if st not in (OK, ERR_TIMEOUT):
         check(st, "winoconv_read_device_error")
     return code.value
+
+
+def probe_mma_rate(cta_pair: bool, a_in_tmem: bool, n_cols: int, n_threads: int, n_mma: int = 512, stream: int = 0):
+    """(clocks per MMA over all issuing threads, issue clocks per MMA of one thread) -- winoconv_probe_mma_rate."""
+    total, issue = ctypes.c_float(0), ctypes.c_float(0)
+    check(lib().winoconv_probe_mma_rate(int(cta_pair), int(a_in_tmem), n_cols, n_threads, n_mma, byref(total),
+                                        byref(issue), stream), "winoconv_probe_mma_rate")
+    return float(total.value), float(issue.value)

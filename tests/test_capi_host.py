@@ -80,7 +80,10 @@ def test_row_piece_plan():
     i3 = capi.plan(d3)
     assert i3.algo == capi.ALGO_ROW and i3.n_pieces == 9
     rgb = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=3, k_out=64, in_size=(224, 224), ker_size=3, pad=1, tile_m=2))
-    assert rgb.algo == capi.ALGO_ROW and rgb.c_pad == 8 and rgb.input_ws_bytes == 4 * 224 * 224 * 8 * 2
+    # RGB with W * C a multiple of eight is read as it lies: no padded copy, no scratch
+    assert rgb.algo == capi.ALGO_ROW and rgb.c_pad == 8 and rgb.input_ws_bytes == 0
+    odd = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=3, k_out=64, in_size=(224, 225), ker_size=3, pad=1, tile_m=2))
+    assert odd.algo == capi.ALGO_ROW and odd.input_ws_bytes == 4 * 224 * 225 * 8 * 2      # 225 x 3 elements: padded copy
     s2 = capi.plan(capi.make_desc(ndim=2, batch=4, c_in=16, k_out=64, in_size=(64, 64), ker_size=7, stride=2, pad=3))
     # stride 2 runs on the row kernel as a stride-1 problem: 4 phases x 16 channels, 4 x 4 kernel (4 rows x 2 windows),
     # input gathered into scratch as [4, 32 + 3, 32 + 3, 64]

@@ -110,3 +110,18 @@ def test_engines_agree_bitwise_inputs():
         outs.append(m)
     torch.cuda.synchronize()
     assert (outs[0] - outs[1]).abs().max().item() <= 1e-4 * outs[0].abs().max().item()
+
+
+def test_mma_rate_probe_reports_the_figures_the_planner_relies_on():
+    """A 128-column MMA from shared memory runs at the tensor pipe's rate (64 clocks); a 64-column one does not
+    (the 4 KB A-operand read keeps it above ~40 clocks) unless A sits in tensor memory."""
+    full, _ = capi.probe_mma_rate(False, False, 128, 2)
+    narrow_smem, _ = capi.probe_mma_rate(False, False, 64, 4)
+    narrow_tmem, _ = capi.probe_mma_rate(False, True, 64, 4)
+    pair_narrow, _ = capi.probe_mma_rate(True, False, 64, 4)
+    print("clocks per MMA: N=128 smem", full, "N=64 smem", narrow_smem, "N=64 tmem", narrow_tmem, "N=64 smem pair", pair_narrow)
+    assert 56 <= full <= 80
+    assert narrow_smem >= 38 and pair_narrow >= 38
+    assert narrow_tmem <= 40
+    with pytest.raises(capi.WinoconvError):
+        capi.probe_mma_rate(False, False, 256, 4)       # four 256-column accumulators do not fit 512 columns
