@@ -429,9 +429,14 @@ def run_gemm_compare(args):
         ut = u.transpose(1, 2).contiguous()
         stream = torch.cuda.current_stream(dev).cuda_stream
         engines = ([("fp32 fma", capi.GEMM_SIMT), ("tf32", capi.GEMM_TF32), ("tf32 x3", capi.GEMM_TF32X3)]
-                   if dt == torch.float32 else [("tcgen05 f16", capi.GEMM_TCGEN05)])
+                   if dt == torch.float32 else [("tcgen05 f16, fp32 products", capi.GEMM_TCGEN05)])
         calls = [(n, (lambda e=e: capi.gemm_batched(engine.dtype_code(dt), capi.F32, e, pos, tiles, c, k, v.data_ptr(),
                                                     u.data_ptr(), m.data_ptr(), stream))) for n, e in engines]
+        if dt != torch.float32:      # what cuBLAS writes here: products rounded to the input dtype
+            m16 = torch.empty(pos, tiles, k, dtype=dt, device=dev)
+            calls.append(("tcgen05 f16, f16 products", lambda: capi.gemm_batched(engine.dtype_code(dt), engine.dtype_code(dt),
+                                                                                  capi.GEMM_TCGEN05, pos, tiles, c, k, v.data_ptr(),
+                                                                                  u.data_ptr(), m16.data_ptr(), stream)))
         calls.append(("torch.bmm (cuBLAS), out in the input dtype", lambda: torch.bmm(v, ut)))
         if dt == torch.float32:
             def bmm_tf32():

@@ -157,25 +157,28 @@ template <int BN, typename TM>
 __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_v,
                                                                const __grid_constant__ CUtensorMap map_u,
                                                                TM *__restrict__ m, int tiles, int c_pad, int k_out,
-                                                               int n_blocks, uint32_t idesc) {
+                                                               int n_blocks, uint32_t idesc, int n_stages) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzled stages need 1024-byte alignment
   uint8_t *ring_ptr = smem_raw + (ring - raw);
-  const uint32_t bars = ring + C::RING_BYTES;    // full[STAGES], empty[STAGES], acc_full
-  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(ring_ptr + C::RING_BYTES + 128);
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ring_ptr + C::RING_BYTES + 132);
+  // The ring holds n_stages stages, no more than the reduction has slabs: a short reduction then leaves room for
+  // several CTAs per SM, whose load, MMA and store phases overlap each other.
+  const int ring_bytes = n_stages * C::STAGE_BYTES;
+  const uint32_t bars = ring + ring_bytes;    // full[n_stages], empty[n_stages], acc_full
+  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(ring_ptr + ring_bytes + 128);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ring_ptr + ring_bytes + 132);
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * C::STAGES);
+  auto empty_bar = [&](int s) { return bars + 8u * (n_stages + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * n_stages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_blk = blockIdx.x % n_blocks, m_blk = blockIdx.x / n_blocks, pos = blockIdx.y;
   const int n_kb = (c_pad + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) {
+    for (int s = 0; s < n_stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -196,8 +199,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     if (lane == 0) {
       int issued = 0;
       for (int kb = 0; kb < n_kb; ++kb) {
-        const int s = kb % C::STAGES;
-        const uint32_t ph = (uint32_t)(kb / C::STAGES) & 1u;
+        const int s = kb % n_stages;
+        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
         if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) break;
         mbar_expect_tx(full_bar(s), (uint32_t)C::STAGE_BYTES);
         const uint32_t a_dst = ring + s * C::STAGE_BYTES;
@@ -208,9 +211,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       if (*abort_word != 0u) {
         // Aborting: nobody may be consuming any more.  Wait (bounded) until every load this thread issued
         // has landed, so no bulk copy is still writing shared memory when the CTA exits.
-        for (int kb = (issued > C::STAGES ? issued - C::STAGES : 0); kb < issued; ++kb) {
+        for (int kb = (issued > n_stages ? issued - n_stages : 0); kb < issued; ++kb) {
           const long long start = clock64();
-          while (!mbar_try_wait(full_bar(kb % C::STAGES), (uint32_t)(kb / C::STAGES) & 1u)) {
+          while (!mbar_try_wait(full_bar(kb % n_stages), (uint32_t)(kb / n_stages) & 1u)) {
             if (clock64() - start > WAIT_LIMIT_CLOCKS) { atomicCAS(&g_device_error, 0u, (unsigned)ERR_DRAIN); break; }
           }
         }
@@ -220,8 +223,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     if (lane == 0) {
       bool ok = true;
       for (int kb = 0; kb < n_kb && ok; ++kb) {
-        const int s = kb % C::STAGES;
-        const uint32_t ph = (uint32_t)(kb / C::STAGES) & 1u;
+        const int s = kb % n_stages;
+        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
         ok = mbar_wait(full_bar(s), ph, abort_word, ERR_MMA_FULL);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -530,6 +533,10 @@ static cudaError_t run(int dtype, int positions, long long tiles, int c_pad, int
     return cudaErrorInvalidValue;
   }
   auto kern = gemm_tcgen05_kernel<BN, TM>;
+  const int n_kb = (c_pad + BK - 1) / BK;
+  int n_stages = n_kb < C::STAGES ? n_kb : C::STAGES;
+  if (n_stages * C::STAGE_BYTES < 4 * 32 * 36 * 4) n_stages = C::STAGES;   // the epilogue stages its rows in the ring
+  const int smem_bytes = n_stages * C::STAGE_BYTES + 1024 + 256;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
   const int n_blocks = (k_out + BN - 1) / BN;
@@ -539,7 +546,7 @@ static cudaError_t run(int dtype, int positions, long long tiles, int c_pad, int
   const uint32_t fmt = dtype == WINOCONV_F16 ? 0u : 1u;
   const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   dim3 grid((unsigned)(m_blocks * n_blocks), (unsigned)positions), block(192);
-  kern<<<grid, block, C::SMEM_BYTES, s>>>(map_v, map_u, (TM *)m, (int)tiles, c_pad, k_out, n_blocks, idesc);
+  kern<<<grid, block, smem_bytes, s>>>(map_v, map_u, (TM *)m, (int)tiles, c_pad, k_out, n_blocks, idesc, n_stages);
   return cudaGetLastError();
 }
 
