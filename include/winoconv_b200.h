@@ -65,8 +65,8 @@ typedef enum winoconv_algo {
                             /* in TMEM; f16 / bf16, strides 1 or 2 (stride 2 runs as a stride-1 problem    */
                             /* over phase channels), kernel <= 7 taps tall (14 at stride 2).  Scratch only */
                             /* to hold the phase-gathered input of a stride-2 layer, or to pad C to a      */
-                            /* multiple of 8 where x cannot be read as it lies (C < 8 with W * C a         */
-                            /* multiple of 8 can) (v_ws, winoconv_plan: input_ws_bytes)                    */
+                            /* multiple of 8, where x cannot be read as it lies (few channels with W * C a */
+                            /* multiple of 8 can, at stride 1 and 2) (v_ws, winoconv_plan: input_ws_bytes) */
 } winoconv_algo_t;
 
 /* epilogue bits, applied inside the output transform */
@@ -194,7 +194,7 @@ WINOCONV_API int winoconv_forward_timed(const winoconv_desc_t *desc, const void 
  *     array; larger layers are refused with WINOCONV_ERR_WORKSPACE and a message stating both sizes.
  *     Layers that fit are walked in as many passes as the array allows.  A ROW layer uses the array for
  *     its whole channel-padded or phase-gathered copy of the input (winoconv_plan: input_ws_bytes; e.g. a
- *     7x7 stride-2 stem on 224 x 224 images passes 32 MiB from batch 80 on) and is refused the same way beyond that:
+ *     7x7 stride-2 stem on 225 x 225 RGB images, whose rows cannot be read as they lie, passes 32 MiB from batch 78 on) and is refused the same way beyond that:
  *     the transformed filter is laid out per algorithm, so re-plan that layer with algo =
  *     WINOCONV_ALGO_FUSED (no scratch at all) or WINOCONV_ALGO_STAGED, transform its filter again and call.
  *   - The first call on each device looks up the array's device address (with that device current) and

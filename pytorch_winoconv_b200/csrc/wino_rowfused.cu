@@ -288,8 +288,12 @@ struct RGeom {
   unsigned epilogue;
   // Few-channel input read as it lies (C < 8, e.g. RGB): the TMA map addresses x as [N, D, H, W * C], a patch row
   // is raw_row_el consecutive elements starting at a multiple of eight, the first patch pixel raw_off elements in.
-  int raw_c;              // 0: the map addresses [N, D, H, W, Cp]; else the caller's channel count
+  // A stride-2 layer over few channels is read the same way: the phase channels of one pixel of the stride-1 problem
+  // are raw_seg = fW * C0 consecutive elements in each of raw_fh = fH consecutive rows of x.
+  int raw_c;              // 0: the map addresses [N, D, H, W, Cp]; else the channels of the stride-1 problem (raw_fh * raw_seg)
   int raw_off, raw_row_el;
+  int raw_seg, raw_fh;    // elements per pixel and row of x (C, or fW * C0); rows of x per patch row (1, or fH)
+  int raw_pd, raw_ph, raw_pw;   // padding of x in its own coordinates (rows, and elements along W), the caller's for a strided layer
 };
 
 template <typename T, int BN, int MB, bool PAIR>
@@ -412,8 +416,8 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             if (lane == 0) {
               mbar_expect_tx(raw_full(s), (uint32_t)sl.raw_bytes);
               if (g.raw_c)   // rows of W * C elements: start at the multiple of eight at or below the first patch pixel
-                tma_load_4d(base + sl.off_raw[s], &map_x, raw_full(s), (cb * g.CBW * 2 - g.pW) * g.raw_c - g.raw_off,
-                            rb * (MB * g.RB) - g.pH, od + kd - g.pD, n);
+                tma_load_4d(base + sl.off_raw[s], &map_x, raw_full(s), cb * g.CBW * 2 * g.raw_seg - g.raw_pw - g.raw_off,
+                            rb * (MB * g.RB) * g.raw_fh - g.raw_ph, od + kd - g.raw_pd, n);
               else
                 tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
                             od + kd - g.pD, n);
@@ -466,12 +470,16 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
             V8<T> o0, o1, o2, o3;
             if (real && g.raw_c) {
               // the caller's few channels, gathered from the raw row into 8-channel vectors (zeros above raw_c)
-              const T *src = reinterpret_cast<const T *>(raw) + (size_t)ir * g.raw_row_el + g.raw_off + (2 * cp + 3 * w) * g.raw_c;
+              // channel ch of the stride-1 problem = element ch % raw_seg of row ch / raw_seg of the pixel's raw rows
+              const T *src = reinterpret_cast<const T *>(raw) + (size_t)(ir * g.raw_fh) * g.raw_row_el + g.raw_off + (2 * cp + 3 * w) * g.raw_seg;
               __align__(16) T dv[4][8];
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
+              for (int c = 0; c < 8; ++c) {
+                const int chn = v * 8 + c;
+                const int rr = chn / g.raw_seg, off = rr * g.raw_row_el + (chn - rr * g.raw_seg);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) dv[i][c] = (c < g.raw_c) ? src[i * g.raw_c + c] : T(0.f);
+                for (int i = 0; i < 4; ++i) dv[i][c] = (chn < g.raw_c) ? src[i * g.raw_seg + off] : T(0.f);
+              }
               const V8<T> d0 = *reinterpret_cast<const V8<T> *>(dv[0]), d1 = *reinterpret_cast<const V8<T> *>(dv[1]);
               const V8<T> d2 = *reinterpret_cast<const V8<T> *>(dv[2]), d3 = *reinterpret_cast<const V8<T> *>(dv[3]);
               o0 = v8_sub<T>(d0, d2); o1 = v8_add<T>(d1, d2); o2 = v8_sub<T>(d2, d1); o3 = v8_sub<T>(d1, d3);
@@ -962,14 +970,30 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   // vectors as they transform, so no padded copy of x is made.  WINOCONV_ROW_RAWC=0 keeps the padding pass.
   static const int rawc_env = [] { const char *v = getenv("WINOCONV_ROW_RAWC"); return v && *v ? atoi(v) : 1; }();
   p.raw_c = 0; p.raw_off = 0; p.raw_row_el = 0;
+  p.raw_seg = 0; p.raw_fh = 1; p.raw_pd = 0; p.raw_ph = 0; p.raw_pw = 0;
   if (d.phases <= 1 && d.C < 8 && ((long long)d.W * d.C) % 8 == 0 && rawc_env != 0) {
     const int off = ((-(d.pW * d.C)) % 8 + 8) % 8;
     const int row_el = (off + p.patch_w * d.C + 7) / 8 * 8;
-    if (row_el <= 256) { p.raw_c = d.C; p.raw_off = off; p.raw_row_el = row_el; }
+    if (row_el <= 256) {
+      p.raw_c = d.C; p.raw_off = off; p.raw_row_el = row_el;
+      p.raw_seg = d.C; p.raw_fh = 1; p.raw_pd = d.pD; p.raw_ph = d.pH; p.raw_pw = d.pW * d.C;
+    }
+  }
+  // Stride 2 in H and / or W over few channels (a 7x7 stride-2 RGB stem: 4 phases x 3 = 12 channels): the phase channels
+  // of a pixel of the stride-1 problem are fW * C0 consecutive elements in each of fH consecutive rows of x, so the same
+  // raw-row patch serves and neither the phase-gathered copy of x nor its scratch is needed.
+  if (d.phases > 1 && d.fD == 1 && d.C <= 32 && ((long long)d.W0 * d.C0) % 8 == 0 && rawc_env != 0) {
+    const int seg = d.fW * d.C0;
+    const int off = ((-(d.pW0 * d.C0)) % 8 + 8) % 8;
+    const int row_el = (off + p.patch_w * seg + 7) / 8 * 8;
+    if (row_el <= 256 && p.patch_h * d.fH <= 256 && (2 * p.CBW * seg) % 8 == 0) {
+      p.raw_c = d.C; p.raw_off = off; p.raw_row_el = row_el;
+      p.raw_seg = seg; p.raw_fh = d.fH; p.raw_pd = d.pD0; p.raw_ph = d.pH0; p.raw_pw = d.pW0 * d.C0;
+    }
   }
   // shared memory: 2 raw patches, 2 slab sets (1 if two do not leave room for 3 filter stages), then as many
   // filter stages as fit (2..8)
-  const int raw_box_bytes = p.raw_c ? p.patch_h * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;
+  const int raw_box_bytes = p.raw_c ? p.patch_h * p.raw_fh * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;
   const int raw_bytes = ((raw_box_bytes + 127) / 128) * 128;
   const int a_bytes = ((4 * p.slab_rows * 64 + 1023) / 1024) * 1024;
   const int b_stage = 4 * (p.pair ? p.BN / 2 : p.BN) * 64;
@@ -1072,8 +1096,9 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   g.patch_h = p.patch_h; g.patch_w = p.patch_w; g.n_chunks = p.n_chunks; g.n_nblocks = p.n_nblocks;
   g.n_items = p.n_items; g.epilogue = d.epilogue;
   g.raw_c = p.raw_c; g.raw_off = p.raw_off; g.raw_row_el = p.raw_row_el;
+  g.raw_seg = p.raw_seg; g.raw_fh = p.raw_fh; g.raw_pd = p.raw_pd; g.raw_ph = p.raw_ph; g.raw_pw = p.raw_pw;
   Smem sl;
-  sl.raw_bytes = p.raw_c ? p.patch_h * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
+  sl.raw_bytes = p.raw_c ? p.patch_h * p.raw_fh * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
   sl.a_bytes = p.a_bytes; sl.b_stage_bytes = p.b_stage_bytes; sl.n_b_stages = p.n_b_stages;
   sl.n_a_bufs = p.n_a_bufs;
   sl.b_group = p.b_group;
@@ -1119,7 +1144,7 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { *detail = "cuTensorMapEncodeTiled unavailable"; return cudaErrorNotSupported; }
   const void *xin = x;
-  if (d.phases > 1) {   // stride 2: gather the polyphase parts into channels (and pad them to a multiple of 8)
+  if (d.phases > 1 && !p.raw_c) {   // stride 2: gather the polyphase parts into channels (and pad them to a multiple of 8)
     if (!pad_ws) { *detail = "phase-gather scratch missing"; return cudaErrorInvalidValue; }
     PhaseGeom q;
     q.N = d.N; q.D = d.D; q.H = d.H; q.W = d.W; q.Cp = p.Cp;
@@ -1148,11 +1173,13 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   }
   const CUtensorMapDataType dt = dtype == WINOCONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap mx, mu;
-  if (p.raw_c) {   // x as it lies: [N, D, H, W * C]
-    const cuuint64_t row = (cuuint64_t)d.W * d.C;
-    const cuuint64_t dims[4] = {row, (cuuint64_t)d.H, (cuuint64_t)d.D, (cuuint64_t)d.N};
-    const cuuint64_t st[3] = {row * 2ull, row * 2ull * d.H, row * 2ull * d.H * d.D};
-    const cuuint32_t box[4] = {(cuuint32_t)p.raw_row_el, (cuuint32_t)p.patch_h, 1u, 1u};
+  if (p.raw_c) {   // x as it lies: [N, D, H, W * C] (the caller's tensor, also for a stride-2 layer)
+    const bool ph = d.phases > 1;
+    const cuuint64_t row = ph ? (cuuint64_t)d.W0 * d.C0 : (cuuint64_t)d.W * d.C;
+    const cuuint64_t hh = ph ? (cuuint64_t)d.H0 : (cuuint64_t)d.H, dd = ph ? (cuuint64_t)d.D0 : (cuuint64_t)d.D;
+    const cuuint64_t dims[4] = {row, hh, dd, (cuuint64_t)d.N};
+    const cuuint64_t st[3] = {row * 2ull, row * 2ull * hh, row * 2ull * hh * dd};
+    const cuuint32_t box[4] = {(cuuint32_t)p.raw_row_el, (cuuint32_t)(p.patch_h * p.raw_fh), 1u, 1u};
     const cuuint32_t es[4] = {1u, 1u, 1u, 1u};
     if (enc(&mx, dt, 4, const_cast<void *>(xin), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {

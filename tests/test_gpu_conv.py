@@ -98,6 +98,12 @@ RAW_FEW_CHANNEL_CASES = [
     (2, 5, 8, (18, 16), (3, 3), 1, 1, 2),          # five channels: offset 3
     (1, 6, 8, (16, 20), (7, 7), 1, 3, 2),          # six channels, 7x7: three windows, offset 6, the widest raw row
     (1, 4, 4, (5, 9, 8), (3, 3, 3), 1, 1, 2),      # 3-D
+    # stride 2 over few channels: the phase channels are gathered from the raw rows in the kernel (no phase-gathered copy)
+    (2, 3, 64, (60, 56), (7, 7), 2, 3, 2),         # RGB stem: 4 phases x 3 channels, 4 x 4 stride-1 kernel
+    (3, 3, 16, (31, 32), (3, 3), 2, 1, 2),         # 3 x 3 at stride 2, odd batch, odd height
+    (1, 4, 16, (35, 36), (5, 5), 2, 0, 2),         # four channels: 16 phase channels fill both vectors (16 x 8 tile blocks)
+    (1, 3, 8, (18, 24), (3, 3), (1, 2), 1, 2),     # stride 2 along W only
+    (1, 2, 8, (19, 20), (5, 3), (2, 1), (2, 1), 2),  # stride 2 along H only
 ]
 ROW_CASES = ROW_CASES + RAW_FEW_CHANNEL_CASES
 

@@ -74,9 +74,9 @@ def test_static_scratch_refuses_oversized_layers():
 
 
 def test_static_scratch_refuses_an_oversized_row_layer_and_names_the_way_out():
-    # 7x7 stride-2 stem, 3 -> 64 at 224 x 224, batch 96: the phase-gathered copy of the input (115 x 115 x 16 channels
-    # per image) is 41 MB > 32 MiB
-    d = capi.make_desc(ndim=2, batch=96, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3)
+    # 7x7 stride-2 stem, 3 -> 64 at 225 x 225 (rows of 675 elements cannot be read as they lie), batch 96: the
+    # phase-gathered copy of the input (116 x 116 x 16 channels per image) is 41 MB > 32 MiB
+    d = capi.make_desc(ndim=2, batch=96, c_in=3, k_out=64, in_size=(225, 225), ker_size=7, stride=2, pad=3)
     assert capi.plan(d).algo == capi.ALGO_ROW and capi.plan(d).input_ws_bytes > capi.STATIC_SCRATCH_BYTES
     with pytest.raises(capi.WinoconvError) as ei:
         capi.forward_static(d, 256, 256, None, 256)
