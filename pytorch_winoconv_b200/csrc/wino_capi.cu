@@ -202,7 +202,7 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
     plan->row = r.phases >= 1 && rowfused_plan(r, &plan->rp);
   }
   if (d->algo == WINOCONV_ALGO_ROW && !plan->row)
-    return fail(WINOCONV_ERR_UNSUPPORTED, "the row-piece kernel needs f16 / bf16, tile_m = 2, strides of 1 or 2, a kernel at most 7 taps tall (14 at stride 2), the tcgen05 engine and fp32 products");
+    return fail(WINOCONV_ERR_UNSUPPORTED, "the row-piece kernel needs f16 / bf16, tile_m = 2, strides of 1 or 2, a patch and slab set that fit shared memory, the tcgen05 engine and fp32 products");
   if (d->algo == WINOCONV_ALGO_FUSED && !fused_ok)
     return fail(WINOCONV_ERR_UNSUPPORTED, "the fused path needs f16 / bf16, tile_m = 2 (or 0 with a kernel other than 2-D 3x3 stride 1), the tcgen05 engine and fp32 products");
   plan->fused = fused_ok && !plan->row && d->algo != WINOCONV_ALGO_STAGED && d->algo != WINOCONV_ALGO_ROW;

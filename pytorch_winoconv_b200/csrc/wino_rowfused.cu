@@ -921,12 +921,12 @@ static EncodeTiledFn get_encode_fn() {
 }  // namespace rowf
 
 // Fills the geometry of the row-piece kernel for the stride-1 problem in `d` (a stride-2 convolution arrives here
-// already folded into phase channels); returns false when it does not apply (kernel taller than 7, or a patch /
-// slab that does not fit shared memory).
+// already folded into phase channels); returns false when it does not apply (a patch / slab set that does not fit
+// shared memory).
 bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   using namespace rowf;
   if (d.sD != 1 || d.sH != 1 || d.sW != 1) return false;
-  if (d.kH > 7 || d.kW > 10 || d.kD > 10) return false;
+  if (d.kH > 10 || d.kW > 10 || d.kD > 10) return false;   // taller kernels: the planner below decides whether patch and slabs fit
   RowPlan p;
   const int Cp = (d.C + 7) / 8 * 8;
   p.Cp = Cp;
