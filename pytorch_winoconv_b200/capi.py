@@ -12,7 +12,8 @@ from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_int, c_int3
                     c_uint64, c_void_p, create_string_buffer)
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libwinoconv_b200.so")
+# WINOCONV_LIB points at another build of the library (e.g. one compiled with different kernel switches)
+LIB_PATH = os.environ.get("WINOCONV_LIB") or os.path.join(_PKG_DIR, "libwinoconv_b200.so")
 
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_NO_DEVICE = range(7)
 F32, F16, BF16 = 0, 1, 2
