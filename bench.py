@@ -722,6 +722,7 @@ def run_ours(args):
     stage_names = ["input_transform", "gemm", "output_transform"]
     per_layer = []
     single_layer = args.workload != "vgg16"
+    esz_io = x_host.element_size()
     # a kernel timed alone is held against the burst figure, one inside a long step against the sustained one;
     # fp32 layers run their products as fp32 FMA: nominal 75 TFLOP/s
     tc_peak_16 = peaks["bf16_tflops"] if single_layer else peaks["bf16_tflops_sustained"]
@@ -754,6 +755,10 @@ def run_ours(args):
         t_tc = info.gemm_flops / (mma_peak * 1e12) * 1e3
         t_hbm = info.algorithmic_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
         t_tc_c = cinfo.gemm_flops / (mma_peak * 1e12) * 1e3
+        # the configuration's compulsory bytes count the convolution's own output (before a fused pool), as its table does
+        b_contract = float(esz_io) * (math.prod(conv.in_shape) + conv._w_keepalive.numel()
+                                      + conv.in_shape[0] * int(conv.desc.k_out) * math.prod(int(v) for v in info.conv_out_size))
+        t_hbm_c = b_contract / (peaks["hbm_gbs"] * 1e9) * 1e3
         per_layer.append({"layer": li + 1, "c": int(conv.desc.c_in), "k": int(conv.desc.k_out),
                           "hw": int(conv.in_shape[-2]), "ms": round(t_ms, 4), "stage_ms": [round(v, 4) for v in st],
                           "launches": n_launch, "algo": ALGO_NAMES[int(info.algo)],
@@ -761,9 +766,9 @@ def run_ours(args):
                           "gemm_tflops": round(info.gemm_flops / (st[1] * 1e-3) / 1e12, 2),
                           "roof_ms": round(max(t_tc, t_hbm), 4), "roof_bound": mma_bound if t_tc >= t_hbm else "hbm",
                           "roof_frac": round(max(t_tc, t_hbm) / t_ms, 4),
-                          "contract": cname, "roof_ms_contract": round(max(t_tc_c, t_hbm), 5),
-                          "roof_bound_contract": "tensor" if t_tc_c >= t_hbm else "hbm",
-                          "roof_frac_contract": round(max(t_tc_c, t_hbm) / t_ms, 4)})
+                          "contract": cname, "roof_ms_contract": round(max(t_tc_c, t_hbm_c), 5),
+                          "roof_bound_contract": "tensor" if t_tc_c >= t_hbm_c else "hbm",
+                          "roof_frac_contract": round(max(t_tc_c, t_hbm_c) / t_ms, 4)})
         h = out
     stage_tot = [sum(l["stage_ms"][i] for l in per_layer) for i in range(3)]
     dom = max(range(3), key=lambda i: stage_tot[i])
@@ -803,7 +808,7 @@ def run_ours(args):
                 "frac": round(achieved / peak, 4),
                 "frac_contract": round(step_roof_ms_contract / sum(l["ms"] for l in per_layer), 4),
                 "frac_contract_note": "sum over layers of max(F_gemm of the algorithm the configuration names / tensor peak, "
-                                      "(x + w + y bytes) / HBM peak), divided by the layers' measured time",
+                                      "(x + w + convolution output bytes) / HBM peak), divided by the layers' measured time",
                 "traffic": traffic, "traffic_source": traffic_source,
                 "kernel": kernel, "launches_per_step": n_dom_launch,
                 "avg_launch_us": round(1e3 * stage_tot[dom] / max(n_dom_launch, 1), 2),

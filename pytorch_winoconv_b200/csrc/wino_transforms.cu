@@ -358,6 +358,15 @@ cudaError_t launch_filter_transform(const Geom &g, int dtype, const void *w, voi
   }
 }
 
+// 2-D F(2,r) pieces with four channels per thread (16-byte accesses in fp32): the patch is 16 x 4 floats, still in registers
+template <typename T>
+static cudaError_t launch_input_v4_2d(const Geom &g, const void *x, void *v, long long t0, int n_tiles, cudaStream_t s) {
+  const long long n = (long long)n_tiles * (g.Cp / 4);
+  dim3 grid((unsigned)((n + 255) / 256), g.n_pieces), block(256);
+  input_transform_kernel<T, 4, 0><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles);
+  return cudaGetLastError();
+}
+
 template <typename T, int VEC>
 static cudaError_t launch_input_tv(const Geom &g, const void *x, void *v, long long t0, int n_tiles, cudaStream_t s) {
   const long long n = (long long)n_tiles * (g.Cp / VEC);
@@ -373,6 +382,13 @@ static cudaError_t launch_input_tv(const Geom &g, const void *x, void *v, long l
 cudaError_t launch_input_transform(const Geom &g, int dtype, const void *x, void *v, long long t0, int n_tiles,
                                    cudaStream_t s) {
   const bool vec = (g.C % 2 == 0);
+  if (mode_of(g) == 0 && g.C % 4 == 0 && g.Cp % 4 == 0) {
+    switch (dtype) {
+      case WINOCONV_F32: return launch_input_v4_2d<float>(g, x, v, t0, n_tiles, s);
+      case WINOCONV_F16: return launch_input_v4_2d<__half>(g, x, v, t0, n_tiles, s);
+      default: return launch_input_v4_2d<__nv_bfloat16>(g, x, v, t0, n_tiles, s);
+    }
+  }
   switch (dtype) {
     case WINOCONV_F32:
       return vec ? launch_input_tv<float, 2>(g, x, v, t0, n_tiles, s) : launch_input_tv<float, 1>(g, x, v, t0, n_tiles, s);
@@ -406,6 +422,12 @@ static cudaError_t launch_output_tv(const Geom &g, const void *m, void *y, const
 template <typename T, typename TM>
 static cudaError_t launch_output_t(const Geom &g, const void *m, void *y, const void *bias, long long t0, int n_tiles,
                                    cudaStream_t s) {
+  if (mode_of(g) == 0 && g.K % 4 == 0) {   // 2-D F(2,r): four channels per thread
+    const long long n = (long long)n_tiles * (g.K / 4);
+    dim3 grid((unsigned)((n + 255) / 256)), block(256);
+    output_transform_kernel<T, TM, 4, 0><<<grid, block, 0, s>>>((const TM *)m, (T *)y, (const T *)bias, g, t0, n_tiles);
+    return cudaGetLastError();
+  }
   if (g.K % 2 == 0) return launch_output_tv<T, TM, 2>(g, m, y, bias, t0, n_tiles, s);
   return launch_output_tv<T, TM, 1>(g, m, y, bias, t0, n_tiles, s);
 }

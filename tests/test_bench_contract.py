@@ -36,3 +36,24 @@ def test_gpu_arm_fails_loudly_without_a_device():
     res = _run(["--steps", "1", "--warmup", "0", "--skip-cpu-baseline"], timeout=120)
     assert res.returncode != 0
     assert "no CPU path" in (res.stderr + res.stdout)
+
+
+@pytest.mark.gpu
+def test_gpu_arm_line_carries_both_roofline_fractions_and_the_error_columns():
+    res = _run(["--workload", "cfg2", "--steps", "3", "--warmup", "3", "--skip-cpu-baseline"], timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["metric"] == "conv_images_per_s" and line["scaling"] == "strong" and line["gpu_launches"] > 0
+    rf = line["roofline"]
+    for key in ("bound", "achieved", "peak", "unit", "frac", "frac_contract", "traffic", "kernel"):
+        assert key in rf
+    assert 0 < rf["frac_contract"] <= 1.5 and 0 < line["step_roofline_frac_contract"] <= 1.5
+    layer = line["layers"][0]
+    assert layer["contract"] == "F(4x4,3x3)" and layer["roof_frac_contract"] > 0 and layer["algo"] in ("staged", "row", "fused")
+    err = line["errors"]["layers"][0]
+    for who in ("engine", "reference_algebra"):
+        assert set(err[who]) == {"E_B", "E_A", "E_C", "P999"}
+    assert err["engine"]["E_B"] <= line["errors"]["tolerance_E_B"]
+    e2e = line["e2e"]
+    assert e2e["h2d_bytes_per_step"] > 0 and e2e["d2h_bytes_per_step"] > 0 and e2e["value"] > 0
+    assert "F(4x4,3x3) staged" in line["config"]["winograd"]
