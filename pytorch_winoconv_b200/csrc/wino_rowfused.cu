@@ -648,13 +648,10 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
               if (ok) { issue_row(); group_end(); ok = group_begin(); }
               if (ok) { issue_row(); group_end(); }
               if (!ok) { alive = false; break; }
-            } else {
-              for (int kh0 = 0; kh0 < kH && alive; kh0 += gk) {
+            } else {                // any other height: single-row groups (gk == 1), one short loop body
+              for (int kh = 0; kh < kH && alive; ++kh) {
                 alive = group_begin();
-                if (alive) {
-                  for (int j = 0; j < gk; ++j) issue_row();
-                  group_end();
-                }
+                if (alive) { issue_row(); group_end(); }
               }
               if (!alive) break;
             }
