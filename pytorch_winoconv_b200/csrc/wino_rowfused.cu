@@ -603,6 +603,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
         const uint32_t acc = tmem_base + (uint32_t)(ab * ACC_COLS);
         uint32_t acc0 = 0u;
         int ch = 0;
+        if (b_resident) { bs = 0; b_lo0 = b_lo_base; }      // a resident filter: every item starts at its first stage
         for (int step = 0; step < steps_per_item && alive; ++step) {
           // a slab with at most 16 real channels (few-channel input, or the tail of C) needs one K = 16 step only
           const bool k2 = ch != tail_chunk;
@@ -638,7 +639,14 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
               if (!b_resident) MMA_COMMIT(b_empty((int)bs));
               if (++bs == b_ring) { bs = 0; b_lo0 = b_lo_base; b_par = b_resident ? 0u : (b_par ^ 1u); }
             };
-            if (gk == 3) {          // kH == 3, all three rows in one group
+            if (b_resident && n_done > 0) {
+              // The whole filter sits in shared memory and has landed: no barrier, no ring bookkeeping -- the rows of an
+              // item are consecutive stages.  These warps run alone on code nothing else keeps in the instruction
+              // cache (~10 clocks an instruction, measured): with one or two MMAs per row the row's bookkeeping, not
+              // the tensor pipe, set the pace of the few-channel and K = 64 layers.
+              if (kH == 3) { issue_row(); issue_row(); issue_row(); }
+              else for (int kh = 0; kh < kH; ++kh) issue_row();
+            } else if (gk == 3) {          // kH == 3, all three rows in one group
               if (!group_begin()) { alive = false; break; }
               issue_row(); issue_row(); issue_row();
               group_end();
