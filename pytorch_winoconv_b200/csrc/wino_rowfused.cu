@@ -465,7 +465,40 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
           if (ok == 0u) { alive = false; break; }
           uint8_t *slab = base_ptr + sl.off_a[as];
           const int slab_bytes = g.slab_rows * 64;
-          for (int row = ptid >> vshift; row < n_tasks; row += N_PROD >> vshift) {
+          const int task_stride = N_PROD >> vshift;
+          int row_first = ptid >> vshift;
+          if (real && !g.raw_c) {
+            // the usual case, two slab rows per round: the eight loads of both rows are in flight together (how fast a
+            // slab set is refilled after the MMAs release it bounds the kernel when only two sets fit shared memory)
+            for (; row_first + task_stride < n_tasks; row_first += 2 * task_stride) {
+              const int row_a = row_first, row_b = row_first + task_stride;
+              const int ir_a = row_a >> cbw_shift, cp_a = row_a - (ir_a << cbw_shift);
+              const int ir_b = row_b >> cbw_shift, cp_b = row_b - (ir_b << cbw_shift);
+              const uint8_t *src_a = raw + ((size_t)(ir_a * g.patch_w + 2 * cp_a + 3 * w) * KC + v * 8) * 2;
+              const uint8_t *src_b = raw + ((size_t)(ir_b * g.patch_w + 2 * cp_b + 3 * w) * KC + v * 8) * 2;
+              V8<T> a0, a1, a2, a3, b0, b1, b2, b3;
+              *reinterpret_cast<uint4 *>(&a0) = *reinterpret_cast<const uint4 *>(src_a);
+              *reinterpret_cast<uint4 *>(&a1) = *reinterpret_cast<const uint4 *>(src_a + KC * 2);
+              *reinterpret_cast<uint4 *>(&a2) = *reinterpret_cast<const uint4 *>(src_a + 2 * KC * 2);
+              *reinterpret_cast<uint4 *>(&a3) = *reinterpret_cast<const uint4 *>(src_a + 3 * KC * 2);
+              *reinterpret_cast<uint4 *>(&b0) = *reinterpret_cast<const uint4 *>(src_b);
+              *reinterpret_cast<uint4 *>(&b1) = *reinterpret_cast<const uint4 *>(src_b + KC * 2);
+              *reinterpret_cast<uint4 *>(&b2) = *reinterpret_cast<const uint4 *>(src_b + 2 * KC * 2);
+              *reinterpret_cast<uint4 *>(&b3) = *reinterpret_cast<const uint4 *>(src_b + 3 * KC * 2);
+              const uint32_t off_a = (uint32_t)row_a * 64u + (uint32_t)((v ^ ((row_a >> 1) & 3)) << 4);
+              const uint32_t off_b = (uint32_t)row_b * 64u + (uint32_t)((v ^ ((row_b >> 1) & 3)) << 4);
+              V8<T> o;
+              o = v8_sub<T>(a0, a2); *reinterpret_cast<uint4 *>(slab + off_a) = *reinterpret_cast<const uint4 *>(&o);
+              o = v8_add<T>(a1, a2); *reinterpret_cast<uint4 *>(slab + slab_bytes + off_a) = *reinterpret_cast<const uint4 *>(&o);
+              o = v8_sub<T>(a2, a1); *reinterpret_cast<uint4 *>(slab + 2 * slab_bytes + off_a) = *reinterpret_cast<const uint4 *>(&o);
+              o = v8_sub<T>(a1, a3); *reinterpret_cast<uint4 *>(slab + 3 * slab_bytes + off_a) = *reinterpret_cast<const uint4 *>(&o);
+              o = v8_sub<T>(b0, b2); *reinterpret_cast<uint4 *>(slab + off_b) = *reinterpret_cast<const uint4 *>(&o);
+              o = v8_add<T>(b1, b2); *reinterpret_cast<uint4 *>(slab + slab_bytes + off_b) = *reinterpret_cast<const uint4 *>(&o);
+              o = v8_sub<T>(b2, b1); *reinterpret_cast<uint4 *>(slab + 2 * slab_bytes + off_b) = *reinterpret_cast<const uint4 *>(&o);
+              o = v8_sub<T>(b1, b3); *reinterpret_cast<uint4 *>(slab + 3 * slab_bytes + off_b) = *reinterpret_cast<const uint4 *>(&o);
+            }
+          }
+          for (int row = row_first; row < n_tasks; row += task_stride) {
             const int ir = row >> cbw_shift, cp = row - (ir << cbw_shift);
             V8<T> o0, o1, o2, o3;
             if (real && g.raw_c) {
