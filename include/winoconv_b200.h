@@ -64,9 +64,10 @@ typedef enum winoconv_algo {
   WINOCONV_ALGO_ROW = 3     /* one tcgen05 kernel, 1x3 pieces: F(2,3) along W, taps along H / depth summed */
                             /* in TMEM; f16 / bf16, strides 1 or 2 (stride 2 runs as a stride-1 problem    */
                             /* over phase channels), any kernel of 1..10 taps per dimension.  Scratch only  */
-                            /* to hold the phase-gathered input of a stride-2 layer, or to pad C to a      */
-                            /* multiple of 8, where x cannot be read as it lies (few channels with W * C a */
-                            /* multiple of 8 can, at stride 1 and 2) (v_ws, winoconv_plan: input_ws_bytes) */
+                            /* where x cannot be read as it lies: to hold the phase-gathered input of a    */
+                            /* stride-2 layer (read in place when C is a multiple of 32, or few channels   */
+                            /* with W * C a multiple of 8), or to pad C to a multiple of 8 (few channels   */
+                            /* with W * C a multiple of 8 need no padding) (v_ws: input_ws_bytes)          */
 } winoconv_algo_t;
 
 /* epilogue bits, applied inside the output transform */

@@ -273,7 +273,7 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
     // the input with its stride-2 phases gathered into channels
     const RowDesc &rd = plan->rd;
     I.input_ws_bytes = I.input_ws_bytes_min =
-        ((rd.phases > 1 || rp.Cp != g.C) && !rp.raw_c) ? (unsigned long long)rd.N * rd.D * rd.H * rd.W * rp.Cp * esz : 0ull;
+        ((rd.phases > 1 || rp.Cp != g.C) && !rp.raw_c && !rp.s2_chunks) ? (unsigned long long)rd.N * rd.D * rd.H * rd.W * rp.Cp * esz : 0ull;
     I.product_ws_bytes = I.product_ws_bytes_min = 0;
     I.block_tiles = I.tiles;
   }

@@ -290,6 +290,11 @@ struct RGeom {
   // is raw_row_el consecutive elements starting at a multiple of eight, the first patch pixel raw_off elements in.
   // A stride-2 layer over few channels is read the same way: the phase channels of one pixel of the stride-1 problem
   // are raw_seg = fW * C0 consecutive elements in each of raw_fh = fH consecutive rows of x.
+  // A stride-2 layer whose channel count is a multiple of 32 is read from the caller's tensor through a map that
+  // traverses H and W with an element stride of 2: one load fetches one polyphase part of a patch, i.e. exactly the
+  // 32-channel step (phase, channel chunk) of the stride-1 problem over phase channels.
+  int s2_chunks;          // 0: off; else 32-channel chunks per polyphase part (C0 / 32)
+  int s2_fh, s2_fw, s2_pd, s2_ph, s2_pw;   // phases per dimension and the caller's padding
   int raw_c;              // 0: the map addresses [N, D, H, W, Cp]; else the channels of the stride-1 problem (raw_fh * raw_seg)
   int raw_off, raw_row_el;
   int raw_seg, raw_fh;    // elements per pixel and row of x (C, or fW * C0); rows of x per patch row (1, or fH)
@@ -418,7 +423,12 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
               if (g.raw_c)   // rows of W * C elements: start at the multiple of eight at or below the first patch pixel
                 tma_load_4d(base + sl.off_raw[s], &map_x, raw_full(s), cb * g.CBW * 2 * g.raw_seg - g.raw_pw - g.raw_off,
                             rb * (MB * g.RB) * g.raw_fh - g.raw_ph, od + kd - g.raw_pd, n);
-              else
+              else if (g.s2_chunks) {   // step ch = (polyphase part, channel chunk): origin of that part in the caller's tensor
+                const int phase = ch / g.s2_chunks, cch = ch - phase * g.s2_chunks;
+                const int ph_h = phase / g.s2_fw, ph_w = phase - ph_h * g.s2_fw;
+                tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), cch * KC, g.s2_fw * (cb * g.CBW * 2) + ph_w - g.s2_pw,
+                            g.s2_fh * (rb * (MB * g.RB)) + ph_h - g.s2_ph, od + kd - g.s2_pd, n);
+              } else
                 tma_load_5d(base + sl.off_raw[s], &map_x, raw_full(s), ch * KC, cb * g.CBW * 2 - g.pW, rb * (MB * g.RB) - g.pH,
                             od + kd - g.pD, n);
             }
@@ -1029,6 +1039,11 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
       p.raw_seg = seg; p.raw_fh = d.fH; p.raw_pd = d.pD0; p.raw_ph = d.pH0; p.raw_pw = d.pW0 * d.C0;
     }
   }
+  // Stride 2 in H and / or W over a multiple of 32 channels: every 32-channel step of the stride-1 problem is one
+  // polyphase part of the caller's tensor, which a tensor map with element strides (fW, fH) loads directly.
+  p.s2_chunks = 0;
+  if (d.phases > 1 && !p.raw_c && d.fD == 1 && d.C0 % KC == 0 && d.fW * p.patch_w <= 256 && d.fH * p.patch_h <= 256 && rawc_env != 0)
+    p.s2_chunks = d.C0 / KC;
   // shared memory: 2 raw patches, 2 slab sets (1 if two do not leave room for 3 filter stages), then as many
   // filter stages as fit (2..8)
   const int raw_box_bytes = p.raw_c ? p.patch_h * p.raw_fh * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;
@@ -1134,6 +1149,7 @@ static cudaError_t launch_rf(const RowDesc &d, const RowPlan &p, const CUtensorM
   g.patch_h = p.patch_h; g.patch_w = p.patch_w; g.n_chunks = p.n_chunks; g.n_nblocks = p.n_nblocks;
   g.n_items = p.n_items; g.epilogue = d.epilogue;
   g.raw_c = p.raw_c; g.raw_off = p.raw_off; g.raw_row_el = p.raw_row_el;
+  g.s2_chunks = p.s2_chunks; g.s2_fh = d.fH; g.s2_fw = d.fW; g.s2_pd = d.pD0; g.s2_ph = d.pH0; g.s2_pw = d.pW0;
   g.raw_seg = p.raw_seg; g.raw_fh = p.raw_fh; g.raw_pd = p.raw_pd; g.raw_ph = p.raw_ph; g.raw_pw = p.raw_pw;
   Smem sl;
   sl.raw_bytes = p.raw_c ? p.patch_h * p.raw_fh * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;   // bytes the TMA box delivers
@@ -1182,7 +1198,7 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { *detail = "cuTensorMapEncodeTiled unavailable"; return cudaErrorNotSupported; }
   const void *xin = x;
-  if (d.phases > 1 && !p.raw_c) {   // stride 2: gather the polyphase parts into channels (and pad them to a multiple of 8)
+  if (d.phases > 1 && !p.raw_c && !p.s2_chunks) {   // stride 2: gather the polyphase parts into channels (and pad them to a multiple of 8)
     if (!pad_ws) { *detail = "phase-gather scratch missing"; return cudaErrorInvalidValue; }
     PhaseGeom q;
     q.N = d.N; q.D = d.D; q.H = d.H; q.W = d.W; q.Cp = p.Cp;
@@ -1222,6 +1238,17 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
     if (enc(&mx, dt, 4, const_cast<void *>(xin), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
       *detail = "cuTensorMapEncodeTiled failed for the few-channel input";
+      return cudaErrorInvalidValue;
+    }
+  } else if (p.s2_chunks) {   // the caller's [N, D0, H0, W0, C0], H and W traversed with the layer's stride
+    const cuuint64_t dims[5] = {(cuuint64_t)d.C0, (cuuint64_t)d.W0, (cuuint64_t)d.H0, (cuuint64_t)d.D0, (cuuint64_t)d.N};
+    const cuuint64_t st[4] = {(cuuint64_t)d.C0 * 2ull, (cuuint64_t)d.C0 * 2ull * d.W0, (cuuint64_t)d.C0 * 2ull * d.W0 * d.H0,
+                              (cuuint64_t)d.C0 * 2ull * d.W0 * d.H0 * d.D0};
+    const cuuint32_t box[5] = {(cuuint32_t)KC, (cuuint32_t)(p.patch_w * d.fW), (cuuint32_t)(p.patch_h * d.fH), 1u, 1u};
+    const cuuint32_t es[5] = {1u, (cuuint32_t)d.fW, (cuuint32_t)d.fH, 1u, 1u};
+    if (enc(&mx, dt, 5, const_cast<void *>(xin), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      *detail = "cuTensorMapEncodeTiled failed for the strided input";
       return cudaErrorInvalidValue;
     }
   } else {

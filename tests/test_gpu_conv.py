@@ -106,6 +106,13 @@ RAW_FEW_CHANNEL_CASES = [
     (1, 4, 16, (35, 36), (5, 5), 2, 0, 2),         # four channels: 16 phase channels fill both vectors (16 x 8 tile blocks)
     (1, 3, 8, (18, 24), (3, 3), (1, 2), 1, 2),     # stride 2 along W only
     (1, 2, 8, (19, 20), (5, 3), (2, 1), (2, 1), 2),  # stride 2 along H only
+    # stride 2 over a multiple of 32 channels: each 32-channel step is one polyphase part, loaded from the caller's tensor
+    # through an element-strided tensor map (no phase-gathered copy)
+    (2, 32, 64, (23, 30), (3, 3), 2, 1, 2),        # odd extents, padding
+    (3, 64, 64, (28, 28), (3, 3), 2, 1, 2),        # a ResNet-style downsampling layer, odd batch
+    (2, 64, 128, (30, 32), (7, 7), 2, 3, 2),       # 7 x 7: 4 x 4 stride-1 kernel over 256 phase channels
+    (1, 32, 32, (17, 20), (3, 3), (2, 1), 1, 2),   # stride 2 along H only
+    (1, 32, 16, (5, 12, 11), (3, 3, 3), (1, 2, 2), 1, 2),   # 3-D, stride 2 in the plane
 ]
 ROW_CASES = ROW_CASES + RAW_FEW_CHANNEL_CASES
 
