@@ -56,7 +56,7 @@ struct RowPlan {
   long long filter_elems, n_items;
   int raw_bytes, a_bytes, b_stage_bytes, n_b_stages, n_a_bufs, smem_total;
   int b_group;   // filter stages per barrier group (1, or 3 = all rows of a 3-row kernel)
-  int s2_chunks;   // > 0: a stride-2 layer read from the caller's tensor through an element-strided tensor map (C0 / 32 chunks per phase)
+  int s2_chunks;   // > 0: a stride-2 layer read from the caller's tensor through an element-strided tensor map (ceil(C0 / 32) chunks per phase)
   int raw_c, raw_off, raw_row_el;   // raw_c > 0: few-channel x is read as it lies (rows of W * C elements)
   int raw_seg, raw_fh, raw_pd, raw_ph, raw_pw;   // elements per pixel and raw row, raw rows per patch row, padding in x's own coordinates
   int pair;   // 1: CTA pairs (two images per work item, one M = 256 MMA over both SMs, filter slabs split between them)

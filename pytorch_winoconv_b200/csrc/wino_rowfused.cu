@@ -839,6 +839,7 @@ __global__ void __launch_bounds__(N_THREADS, 1) rowfused_kernel(const __grid_con
 // tap (fD * kd + phase_d, fH * kh + phase_h, fW * kw + phase_w) of the caller's kernel (zero beyond its extent).
 struct FilterPhases {
   int on, fD, fH, fW, C0, kD0, kH0, kW0;
+  int Cs;     // channel stride between polyphase parts in the phase-channel order (C0, or C0 rounded up to 32)
 };
 template <typename T>
 __global__ void __launch_bounds__(256) rowfused_filter_kernel(const T *__restrict__ wgt, T *__restrict__ u, int C, int Cp,
@@ -854,17 +855,19 @@ __global__ void __launch_bounds__(256) rowfused_filter_kernel(const T *__restric
   const int kh = (int)(rem % kH);
   const int kd = (int)(rem / kH);
   float a[3] = {0.f, 0.f, 0.f}, o[4];
-  if (c < C) {
-    // the caller's channel and kernel extents, and this element's phase offsets
-    int c0 = c, C0 = C, eD = kD, eH = kH, eW = kW, fD = 1, fH = 1, fW = 1, pd = 0, phh = 0, pw = 0;
-    if (ph.on) {
-      C0 = ph.C0; eD = ph.kD0; eH = ph.kH0; eW = ph.kW0; fD = ph.fD; fH = ph.fH; fW = ph.fW;
-      int phase = c / C0;
-      c0 = c - phase * C0;
-      pw = phase % fW; phase /= fW;
-      phh = phase % fH; phase /= fH;
-      pd = phase;
-    }
+  // the caller's channel and kernel extents, and this element's phase offsets
+  int c0 = c, C0 = C, eD = kD, eH = kH, eW = kW, fD = 1, fH = 1, fW = 1, pd = 0, phh = 0, pw = 0;
+  bool valid = c < C;
+  if (ph.on) {
+    C0 = ph.C0; eD = ph.kD0; eH = ph.kH0; eW = ph.kW0; fD = ph.fD; fH = ph.fH; fW = ph.fW;
+    int phase = c / ph.Cs;
+    c0 = c - phase * ph.Cs;
+    valid = phase < fD * fH * fW && c0 < C0;
+    pw = phase % fW; phase /= fW;
+    phh = phase % fH; phase /= fH;
+    pd = phase;
+  }
+  if (valid) {
     const int td = fD * kd + pd, th = fH * kh + phh;
 #pragma unroll
     for (int t = 0; t < 3; ++t) {
@@ -976,7 +979,7 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   if (d.sD != 1 || d.sH != 1 || d.sW != 1) return false;
   if (d.kH > 10 || d.kW > 10 || d.kD > 10) return false;   // taller kernels: the planner below decides whether patch and slabs fit
   RowPlan p;
-  const int Cp = (d.C + 7) / 8 * 8;
+  int Cp = (d.C + 7) / 8 * 8;
   p.Cp = Cp;
   p.PW = (d.kW + 2) / 3;
   // Work item: MB tile blocks stacked along H x BN output channels, MB * BN <= 128 (the 512 TMEM columns hold
@@ -1042,8 +1045,18 @@ bool rowfused_plan(const RowDesc &d, RowPlan *out) {
   // Stride 2 in H and / or W over a multiple of 32 channels: every 32-channel step of the stride-1 problem is one
   // polyphase part of the caller's tensor, which a tensor map with element strides (fW, fH) loads directly.
   p.s2_chunks = 0;
-  if (d.phases > 1 && !p.raw_c && d.fD == 1 && d.C0 % KC == 0 && d.fW * p.patch_w <= 256 && d.fH * p.patch_h <= 256 && rawc_env != 0)
-    p.s2_chunks = d.C0 / KC;
+  // A channel count that is a multiple of 8 but not of 32 gets its polyphase parts 32-aligned in the phase-channel
+  // order (the map's zero fill and zero filter channels pad each part).
+  // Taken while the padding adds at most a third to the reduction.
+  const int s2_padded_chunks = d.phases * ((d.C0 + KC - 1) / KC);
+  if (d.phases > 1 && !p.raw_c && d.fD == 1 && d.C0 % 8 == 0 && d.fW * p.patch_w <= 256 && d.fH * p.patch_h <= 256 &&
+      3 * s2_padded_chunks <= 4 * p.n_chunks && rawc_env != 0) {
+    p.s2_chunks = (d.C0 + KC - 1) / KC;
+    Cp = d.phases * p.s2_chunks * KC;
+    p.Cp = Cp;
+    p.n_chunks = Cp / KC;
+    p.filter_elems = (long long)p.slabs * d.K * Cp;
+  }
   // shared memory: 2 raw patches, 2 slab sets (1 if two do not leave room for 3 filter stages), then as many
   // filter stages as fit (2..8)
   const int raw_box_bytes = p.raw_c ? p.patch_h * p.raw_fh * p.raw_row_el * 2 : p.patch_h * p.patch_w * KC * 2;
@@ -1111,6 +1124,7 @@ cudaError_t launch_rowfused_filter_transform(const RowDesc &d, const RowPlan &p,
   rowf::FilterPhases ph = {};
   if (d.phases > 1) {
     ph.on = 1; ph.fD = d.fD; ph.fH = d.fH; ph.fW = d.fW; ph.C0 = d.C0; ph.kD0 = d.kD0; ph.kH0 = d.kH0; ph.kW0 = d.kW0;
+    ph.Cs = p.s2_chunks ? p.s2_chunks * rowf::KC : d.C0;
   }
   if (dtype == WINOCONV_F16)
     rowf::rowfused_filter_kernel<__half><<<blocks, 256, 0, s>>>((const __half *)w, (__half *)u, d.C, p.Cp, d.K, d.kD, d.kH, d.kW, p.PW, d.weight_layout, ph);
@@ -1213,7 +1227,7 @@ cudaError_t launch_rowfused_forward(const RowDesc &d, const RowPlan &p, int dtyp
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { *detail = "phase gather launch failed"; return e; }
     xin = pad_ws;
-  } else if (p.Cp != d.C && !p.raw_c) {   // channels not a multiple of 8: TMA needs 16-byte pixel strides, so pad into scratch first
+  } else if (p.Cp != d.C && !p.raw_c && !p.s2_chunks) {   // channels not a multiple of 8: TMA needs 16-byte pixel strides, so pad into scratch first
     if (!pad_ws) { *detail = "channel padding scratch missing"; return cudaErrorInvalidValue; }
     const long long pixels = (long long)d.N * d.D * d.H * d.W;
     const unsigned blocks = (unsigned)((pixels * (p.Cp / 8) + 255) / 256);

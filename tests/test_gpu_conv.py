@@ -113,6 +113,10 @@ RAW_FEW_CHANNEL_CASES = [
     (2, 64, 128, (30, 32), (7, 7), 2, 3, 2),       # 7 x 7: 4 x 4 stride-1 kernel over 256 phase channels
     (1, 32, 32, (17, 20), (3, 3), (2, 1), 1, 2),   # stride 2 along H only
     (1, 32, 16, (5, 12, 11), (3, 3, 3), (1, 2, 2), 1, 2),   # 3-D, stride 2 in the plane
+    # ... and over a multiple of 8: each part's channels are padded to 32 by the map's zero fill and zero filter channels
+    (2, 24, 32, (23, 30), (3, 3), 2, 1, 2),        # 24 of 32
+    (1, 48, 64, (20, 22), (3, 3), 2, 1, 2),        # 48 of 64: a full step and a half one per part
+    (1, 72, 16, (17, 18), (5, 5), 2, 2, 2),        # 72 of 96, 5 x 5
 ]
 ROW_CASES = ROW_CASES + RAW_FEW_CHANNEL_CASES
 
