@@ -87,7 +87,8 @@ typedef struct winoconv_desc {
   int32_t pad[3];        /* symmetric zero padding per dimension, applied in-kernel          */
   int32_t tile_m;        /* Winograd output block: 0 = auto (2 where a single-kernel path
                           * takes the layer, else 4 for 2-D 3x3 stride 1), 2 = F(2,r),
-                          * 4 = F(4x4,3x3)                                               */
+                          * 4 = F(4x4,3x3), 6 = F(6x6,3x3) (f32 operands with the SIMT or
+                          * TF32X3 engine only: 64 positions, 1.78 multiplies per output) */
   int32_t dtype;         /* winoconv_dtype_t of x, weights, y and of the transformed filter  */
   int32_t weight_layout; /* winoconv_wlayout_t                                               */
   uint32_t epilogue;     /* WINOCONV_EPI_* bits                                              */

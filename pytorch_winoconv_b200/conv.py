@@ -244,7 +244,7 @@ class Conv2d(_WinoConvMixin, nn.Conv2d):
 
     Extra keyword arguments: ``compute_dtype`` (default ``torch.float16`` as upstream, ``None`` keeps the
     input's dtype; fp32 runs its products as three tf32 tensor-core products of a hi / lo split), ``activation`` (``None`` / ``"relu"``),
-    ``pool`` (``None`` / ``2``), ``tile_m`` (0 auto, 2, 4) and ``algo`` (``capi.ALGO_*``).
+    ``pool`` (``None`` / ``2``), ``tile_m`` (0 auto, 2, 4; 6 for fp32 layers) and ``algo`` (``capi.ALGO_*``).
     """
 
     _nd = 2

@@ -104,14 +104,18 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
                                        d->gemm_engine != WINOCONV_GEMM_SIMT && d->product_dtype == WINOCONV_F32;
   int tile_m = d->tile_m;
   if (tile_m == 0) tile_m = (f43_ok && !single_kernel_candidate) ? 4 : 2;
-  if (tile_m != 2 && tile_m != 4) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m must be 0, 2 or 4");
+  if (tile_m != 2 && tile_m != 4 && tile_m != 6) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m must be 0, 2, 4 or 6");
   if (tile_m == 4 && !f43_ok) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 4 is F(4x4,3x3): 2-D, 3x3 kernel, stride 1 only");
+  if (tile_m == 6 && !f43_ok) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 6 is F(6x6,3x3): 2-D, 3x3 kernel, stride 1 only");
+  // F(6x6,3x3) with 16-bit or single-tf32 operands sits at 5e-2 of the output scale (measured), beyond the 2e-2 bound
+  if (tile_m == 6 && (d->dtype != WINOCONV_F32 || d->gemm_engine == WINOCONV_GEMM_TF32))
+    return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 6 (F(6x6,3x3)) takes f32 operands with fp32-class products (SIMT or TF32X3 engine)");
   int m[3], out[3], nt[3];
   // A depth of one tap at stride 1 (every 2-D conv) is not tiled: no dummy F(2,1) along depth, which is
   // what doubles the positions of every 2-D call in the reference (dwm.py:117).
   m[0] = (ks[0] == 1 && st[0] == 1) ? 1 : 2;
   m[1] = tile_m; m[2] = tile_m;
-  if (m[0] == 2 && tile_m == 4) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 4 with a depth kernel");
+  if (m[0] == 2 && tile_m != 2) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 4 or 6 with a depth kernel");
   for (int i = 0; i < 3; ++i) {
     out[i] = (in[i] + 2 * pd[i] - ks[i]) / st[i] + 1;
     nt[i] = (out[i] + m[i] - 1) / m[i];

@@ -268,6 +268,52 @@ template <> struct Xf<4, 3> {
   }
 };
 
+// F(6,3) on the customary points (0, +-1, +-2, +-1/2, inf): B^T and A^T are dyadic, G carries the 1 / f_p factors.
+// Its transforms amplify the rounding of the transformed operands ~5e-2 of the output scale with 16-bit (or tf32)
+// operands -- measured on N(0,1) data over 64 channels -- against 8e-6 with fp32 operands, so only fp32 layers
+// whose products keep fp32-class accuracy (FMA or three tf32 products) use it.
+template <> struct Xf<6, 3> {
+  static constexpr int ALPHA = 8;
+  template <int S> static __device__ __forceinline__ void bt(float *d) {
+    float d0 = d[0], d1 = d[S], d2 = d[2 * S], d3 = d[3 * S], d4 = d[4 * S], d5 = d[5 * S], d6 = d[6 * S], d7 = d[7 * S];
+    float e1 = fmaf(-4.25f, d4, d2 + d6), o1 = fmaf(-4.25f, d3, d1 + d5);
+    float e2 = fmaf(0.25f, d2, fmaf(-1.25f, d4, d6)), o2 = fmaf(0.5f, d1, fmaf(-2.5f, d3, 2.f * d5));
+    float e3 = fmaf(4.f, d2, fmaf(-5.f, d4, d6)), o3 = fmaf(2.f, d1, fmaf(-2.5f, d3, 0.5f * d5));
+    d[0] = fmaf(5.25f, d4 - d2, d0 - d6);
+    d[S] = e1 + o1;
+    d[2 * S] = e1 - o1;
+    d[3 * S] = e2 + o2;
+    d[4 * S] = e2 - o2;
+    d[5 * S] = e3 + o3;
+    d[6 * S] = e3 - o3;
+    d[7 * S] = fmaf(5.25f, d3 - d5, d7 - d1);
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void g(const float *w, float *u) {
+    float w0 = w[0], w1 = w[SI], w2 = w[2 * SI];
+    float s1 = (-2.f / 9.f) * (w0 + w2), t1 = (-2.f / 9.f) * w1;
+    float s2 = fmaf(1.f / 90.f, w0, (2.f / 45.f) * w2), t2 = (1.f / 45.f) * w1;
+    float s3 = fmaf(32.f / 45.f, w0, (8.f / 45.f) * w2), t3 = (16.f / 45.f) * w1;
+    u[0] = w0;
+    u[SO] = s1 + t1;
+    u[2 * SO] = s1 - t1;
+    u[3 * SO] = s2 + t2;
+    u[4 * SO] = s2 - t2;
+    u[5 * SO] = s3 + t3;
+    u[6 * SO] = s3 - t3;
+    u[7 * SO] = w2;
+  }
+  template <int SI, int SO> static __device__ __forceinline__ void at(const float *p, float *y) {
+    float p0 = p[0], p1 = p[SI], p2 = p[2 * SI], p3 = p[3 * SI], p4 = p[4 * SI], p5 = p[5 * SI], p6 = p[6 * SI], p7 = p[7 * SI];
+    float s12 = p1 + p2, d12 = p1 - p2, s34 = p3 + p4, d34 = p3 - p4, s56 = p5 + p6, d56 = p5 - p6;
+    y[0] = p0 + s12 + s34 + s56;
+    y[SO] = fmaf(2.f, d34, fmaf(0.5f, d56, d12));
+    y[2 * SO] = fmaf(4.f, s34, fmaf(0.25f, s56, s12));
+    y[3 * SO] = fmaf(8.f, d34, fmaf(0.125f, d56, d12));
+    y[4 * SO] = fmaf(16.f, s34, fmaf(0.0625f, s56, s12));
+    y[5 * SO] = fmaf(32.f, d34, fmaf(0.03125f, d56, d12)) + p7;
+  }
+};
+
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 }  // namespace wino

@@ -18,10 +18,12 @@ namespace wino {
 
 // MODE selects the output block per dimension (uniform for a launch):
 //   0: (1,2,2)  2-D F(2,r) pieces        1: (2,2,2)  3-D F(2,r) pieces        2: (1,4,4)  2-D F(4x4,3x3)
+//   3: (1,6,6)  2-D F(6x6,3x3), fp32 only
 template <int MODE> struct ModeM;
 template <> struct ModeM<0> { static constexpr int MD = 1, MH = 2, MW = 2; };
 template <> struct ModeM<1> { static constexpr int MD = 2, MH = 2, MW = 2; };
 template <> struct ModeM<2> { static constexpr int MD = 1, MH = 4, MW = 4; };
+template <> struct ModeM<3> { static constexpr int MD = 1, MH = 6, MW = 6; };
 
 // Nested switch over the taps of a piece; BODY(RD, RH, RW) is expanded with literals.
 #define WINO_SW_W(RD, RH, BODY)                                   \
@@ -336,7 +338,11 @@ __global__ void __launch_bounds__(256) output_transform_kernel(const TM *__restr
 // ------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------
-static inline int mode_of(const Geom &g) { return g.mH == 4 ? 2 : (g.mD == 2 ? 1 : 0); }
+static inline int mode_of(const Geom &g) { return g.mH == 6 ? 3 : (g.mH == 4 ? 2 : (g.mD == 2 ? 1 : 0)); }
+
+// F(6x6,3x3) is instantiated for fp32 only (the planner refuses it for 16-bit operands)
+template <typename T> constexpr bool kHasF63 = false;
+template <> constexpr bool kHasF63<float> = true;
 
 template <typename T>
 static cudaError_t launch_filter_t(const Geom &g, const void *w, void *u, cudaStream_t s) {
@@ -345,7 +351,11 @@ static cudaError_t launch_filter_t(const Geom &g, const void *w, void *u, cudaSt
   switch (mode_of(g)) {
     case 0: filter_transform_kernel<T, 0><<<grid, block, 0, s>>>((const T *)w, (T *)u, g); break;
     case 1: filter_transform_kernel<T, 1><<<grid, block, 0, s>>>((const T *)w, (T *)u, g); break;
-    default: filter_transform_kernel<T, 2><<<grid, block, 0, s>>>((const T *)w, (T *)u, g); break;
+    case 2: filter_transform_kernel<T, 2><<<grid, block, 0, s>>>((const T *)w, (T *)u, g); break;
+    default:
+      if constexpr (kHasF63<T>) filter_transform_kernel<T, 3><<<grid, block, 0, s>>>((const T *)w, (T *)u, g);
+      else return cudaErrorInvalidValue;
+      break;
   }
   return cudaGetLastError();
 }
@@ -374,14 +384,19 @@ static cudaError_t launch_input_tv(const Geom &g, const void *x, void *v, long l
   switch (mode_of(g)) {
     case 0: input_transform_kernel<T, VEC, 0><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles); break;
     case 1: input_transform_kernel<T, VEC, 1><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles); break;
-    default: input_transform_kernel<T, VEC, 2><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles); break;
+    case 2: input_transform_kernel<T, VEC, 2><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles); break;
+    default:
+      if constexpr (kHasF63<T>) input_transform_kernel<T, VEC, 3><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles);
+      else return cudaErrorInvalidValue;
+      break;
   }
   return cudaGetLastError();
 }
 
 cudaError_t launch_input_transform(const Geom &g, int dtype, const void *x, void *v, long long t0, int n_tiles,
                                    cudaStream_t s) {
-  const bool vec = (g.C % 2 == 0);
+  // F(6x6,3x3) keeps an 8 x 8 patch per channel in registers: one channel per thread (two would leave one block per SM)
+  const bool vec = (g.C % 2 == 0) && mode_of(g) != 3;
   if (mode_of(g) == 0 && g.C % 4 == 0 && g.Cp % 4 == 0) {
     switch (dtype) {
       case WINOCONV_F32: return launch_input_v4_2d<float>(g, x, v, t0, n_tiles, s);
@@ -412,8 +427,14 @@ static cudaError_t launch_output_tv(const Geom &g, const void *m, void *y, const
     case 1:
       output_transform_kernel<T, TM, VEC, 1><<<grid, block, 0, s>>>((const TM *)m, (T *)y, (const T *)bias, g, t0, n_tiles);
       break;
-    default:
+    case 2:
       output_transform_kernel<T, TM, VEC, 2><<<grid, block, 0, s>>>((const TM *)m, (T *)y, (const T *)bias, g, t0, n_tiles);
+      break;
+    default:
+      if constexpr (kHasF63<T>)
+        output_transform_kernel<T, TM, VEC, 3><<<grid, block, 0, s>>>((const TM *)m, (T *)y, (const T *)bias, g, t0, n_tiles);
+      else
+        return cudaErrorInvalidValue;
       break;
   }
   return cudaGetLastError();
@@ -428,7 +449,7 @@ static cudaError_t launch_output_t(const Geom &g, const void *m, void *y, const 
     output_transform_kernel<T, TM, 4, 0><<<grid, block, 0, s>>>((const TM *)m, (T *)y, (const T *)bias, g, t0, n_tiles);
     return cudaGetLastError();
   }
-  if (g.K % 2 == 0) return launch_output_tv<T, TM, 2>(g, m, y, bias, t0, n_tiles, s);
+  if (g.K % 2 == 0 && mode_of(g) != 3) return launch_output_tv<T, TM, 2>(g, m, y, bias, t0, n_tiles, s);
   return launch_output_tv<T, TM, 1>(g, m, y, bias, t0, n_tiles, s);
 }
 

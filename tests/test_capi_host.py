@@ -28,6 +28,7 @@ BASELINE_CONFIGS = [
     # name, kwargs, expected (positions, pieces, tiles)
     ("cfg1", dict(ndim=2, batch=8, c_in=64, k_out=64, in_size=(56, 56), ker_size=3, pad=1, tile_m=2, dtype=capi.F32), (16, 1, 6272)),
     ("cfg2", dict(ndim=2, batch=32, c_in=256, k_out=256, in_size=(28, 28), ker_size=3, pad=1, tile_m=4), (36, 1, 1568)),
+    ("cfg1 as F(6x6,3x3)", dict(ndim=2, batch=8, c_in=64, k_out=64, in_size=(56, 56), ker_size=3, pad=1, tile_m=6, dtype=capi.F32), (64, 1, 800)),
     ("cfg3a", dict(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3, algo=capi.ALGO_STAGED), (100, 9, 200704)),
     ("cfg3b", dict(ndim=2, batch=32, c_in=128, k_out=128, in_size=(56, 56), ker_size=5, pad=2, algo=capi.ALGO_STAGED), (49, 4, 25088)),
     ("cfg4", dict(ndim=3, batch=8, c_in=64, k_out=64, in_size=(16, 56, 56), ker_size=3, pad=1, algo=capi.ALGO_STAGED), (64, 1, 50176)),

@@ -249,6 +249,48 @@ def test_cfg1_fp32_product_arithmetic_table():
         assert table[("tf32", tm)] <= 2e-2          # bounded, but (measured) over the fp32 tolerance
 
 
+F63_CASES = [
+    # N, C, K, spatial, padding
+    (2, 8, 8, (12, 12), 1),            # 2 x 2 whole tiles
+    (1, 16, 8, (13, 17), 0),           # no padding, ragged last tiles (11 x 15 outputs)
+    (2, 3, 5, (9, 20), 1),             # C, K not vector multiples; a single tile row
+    (1, 7, 9, (30, 7), (2, 1)),        # wider padding than the kernel needs, narrow image
+    (8, 64, 64, (56, 56), 1),          # configs[0]'s layer
+]
+
+
+@pytest.mark.parametrize("n,c,k,sp,pad", F63_CASES)
+@pytest.mark.parametrize("eng", [capi.GEMM_SIMT, capi.GEMM_TF32X3])
+def test_f63_fp32(n, c, k, sp, pad, eng):
+    """F(6x6,3x3) (64 positions, 1.78 multiplies per output; the reference stops at F(2,3)): fp32 operands with fp32 FMA
+    or three-tf32 products hold the fp32 bound."""
+    x = seeded((n, c) + sp, 21)
+    w = wo.kaiming_normal((k, c, 3, 3), 22)
+    y, conv = run_engine(x, w, padding=pad, tile_m=6, gemm_engine=eng)
+    assert conv.info.algo == capi.ALGO_STAGED and conv.info.positions == 64 and list(conv.info.tile_m) == [1, 6, 6]
+    err = check_against_oracle(x, w, y, padding=pad)
+    assert err["E_B"] <= 2e-4, err       # measured 1e-5-class; well inside the 1e-3 contract
+
+
+def test_f63_epilogue_and_refusals():
+    x = seeded((2, 16, 14, 16), 23)
+    w = wo.kaiming_normal((24, 16, 3, 3), 24)
+    b = seeded((24,), 25)
+    o = torch.relu(wo.direct_conv_f64(x, w, padding=1) + b.double().view(1, -1, 1, 1))
+    y, _ = run_engine(x, w, padding=1, tile_m=6, bias=b, relu=True)
+    assert wo.error_metrics(y, o)["E_A"] < 1e-4
+    y, _ = run_engine(x, w, padding=1, tile_m=6, bias=b, relu=True, pool2=True)
+    op = torch.nn.functional.max_pool2d(o, 2)
+    assert tuple(y.shape) == tuple(op.shape) and wo.error_metrics(y, op)["E_A"] < 1e-4
+    for kw in (dict(dtype=capi.F16), dict(dtype=capi.F32, gemm_engine=capi.GEMM_TF32), dict(dtype=capi.F32, ker_size=5),
+               dict(dtype=capi.F32, stride=2)):
+        args = dict(ndim=2, batch=1, c_in=8, k_out=8, in_size=(12, 12), ker_size=3, stride=1, pad=1, tile_m=6)
+        args.update(kw)
+        with pytest.raises(capi.WinoconvError) as ei:
+            capi.plan(capi.make_desc(**args))
+        assert ei.value.status == capi.ERR_UNSUPPORTED
+
+
 @pytest.mark.parametrize("product_dtype", [None, torch.float16])
 @pytest.mark.parametrize("seed", [0, 17])
 def test_cfg2_fp16_f43(product_dtype, seed):

@@ -116,6 +116,17 @@ def test_matrix_conv_routes(chain, block):
     assert wo.error_metrics(y16, o)["E_B"] < 2e-2
 
 
+def test_matrix_conv_output_block_6_is_fp32_only():
+    from pytorch_winoconv_b200 import capi, matrix_conv
+    x = seeded((2, 16, 13, 12), 14)
+    w = wo.kaiming_normal((8, 16, 3, 3), 15)
+    o = wo.direct_conv_f64(x, w, padding=1)
+    y32 = matrix_conv.conv32(x.cuda(), w.cuda(), padding=(1, 1), output_block=6).cpu()
+    assert wo.error_metrics(y32, o)["E_B"] < 1e-3
+    with pytest.raises(capi.WinoconvError):      # F(6x6,3x3) over fp16 operands cannot hold the 2e-2 bound: refused, not approximated
+        matrix_conv.conv16(x.cuda(), w.cuda(), padding=(1, 1), output_block=6)
+
+
 def test_matrix_conv3d_and_nd_and_dwm_convnd():
     from pytorch_winoconv_b200 import dwm_convnd, matrix_conv3d, matrix_convnd
     x = seeded((1, 8, 6, 7, 8), 17)
