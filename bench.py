@@ -785,10 +785,10 @@ def run_ours(args):
         if io_dtype == torch.float32:
             peak, bound = product_peak(layers[0])
             unit = "TFLOP/s"
-            kernel = "gemm_simt_kernel" if bound == "fp32-fma" else "gemm_tf32_kernel"
+            kernel = "gemm_simt_kernel" if bound == "fp32-fma" else "gemm_persistent_kernel"
         else:
             peak, unit, bound = tc_peak_16, "TFLOP/s", "tensor"
-            kernel = "rowfused_kernel" if is_row else ("fused23_kernel" if is_fused else "gemm_tcgen05_kernel")
+            kernel = "rowfused_kernel" if is_row else ("fused23_kernel" if is_fused else "gemm_persistent_kernel")
     else:
         if dom == 0:   # algorithmic bytes of the input transform: it must read x once
             alg = sum(float(esz) * math.prod(c.in_shape) for c in layers)

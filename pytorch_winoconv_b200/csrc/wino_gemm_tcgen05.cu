@@ -2,17 +2,18 @@
 //
 //     m[p][t][k] = sum_c v[p][t][c] * u[p][k][c]        fp16 / bf16 in, fp32 accumulate
 //
-// One CTA computes a 128 (tiles) x BN (output channels) block of one Winograd position.
+// Persistent: one CTA per SM walks 128 (tiles) x BN (output channels) blocks of the positions with a fixed stride.
 //   warp 0      TMA producer: cp.async.bulk.tensor.3d loads of the V slab [128 x 64] and the U slab
-//               [BN x 64] (both reduction-major, 128-byte swizzle) into a ring of shared-memory stages,
-//               completion on an mbarrier per stage.  No cluster, no multicast.
-//   warp 1      owns TMEM (tcgen05.alloc / dealloc) and issues tcgen05.mma.cta_group::1.kind::f16
-//               from one thread: four K=16 MMAs per 64-wide slab, accumulator 128 lanes x BN fp32 columns
-//               in TMEM; tcgen05.commit hands each stage back to the producer and finally signals the
-//               epilogue.
-//   warps 2..5  epilogue: tcgen05.ld of their 32-lane quarter, 32 columns at a time, transposed through
-//               shared memory (the stage ring is idle by then) so that each store instruction writes whole
-//               128-byte rows of M.
+//               [BN x 64] (both reduction-major, 128-byte swizzle) into a ring of shared-memory stages that runs on
+//               across blocks, completion on an mbarrier per stage.  No cluster, no multicast.
+//   warp 1      owns TMEM (tcgen05.alloc / dealloc) and issues tcgen05.mma.cta_group::1.kind::f16 (or kind::tf32)
+//               from one thread: four MMAs per 128-byte slab, accumulator 128 lanes x BN fp32 columns, two of
+//               them in TMEM; tcgen05.commit hands each stage back to the producer and each finished accumulator
+//               to the epilogue.
+//   warps 2..9  epilogue: tcgen05.ld of their 32-lane quarter (two warps per quarter, alternate chunks), 32 columns at a time, transposed through
+//               shared memory so that each store instruction writes whole 128-byte rows of M; the accumulator
+//               goes back to warp 1 as soon as its last columns are in registers.
+//   warps 10..13 (three-tf32-product kind only) split every landed stage into hi / lo parts in shared memory.
 // Ragged edges need no special code on the load side: TMA zero-fills rows beyond `tiles` / `k_out` and
 // channels beyond `c_pad`; the epilogue masks its stores.
 //
@@ -23,6 +24,9 @@
 // Stands in for forwardAssign + cublasHgemmBatched (src/base_conv_launchers_half.cu:218-236; the
 // reference accumulates in fp16 there) and cublasSgemmBatched (src/base_conv_launchers.cu:349-367).
 #include <cuda.h>
+
+#include <map>
+#include <mutex>
 
 #include "wino_common.cuh"
 #include "wino_launch.h"
@@ -36,20 +40,9 @@ namespace tc {
 
 constexpr int BM = 128;      // rows (tiles) per CTA == TMEM lanes
 constexpr int BK = 64;       // reduction slab: 64 x 2 B = one 128-byte swizzle row
-constexpr int UMMA_K = 16;   // reduction depth of one kind::f16 MMA
-constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;  // ~1 s at 1.9 GHz
 
 enum ErrCode : unsigned { ERR_PRODUCER_EMPTY = 0x101, ERR_MMA_FULL = 0x102, ERR_EPI_ACC = 0x103, ERR_DRAIN = 0x104 };
-
-template <int BN> struct Cfg {
-  static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
-  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static_assert(RING_BYTES >= 4 * 32 * 36 * 4, "epilogue staging must fit in the ring");
-};
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -153,160 +146,16 @@ template <typename H> struct StoreRow16 {
 template <> struct StoreRow<__half> : StoreRow16<__half> {};
 template <> struct StoreRow<__nv_bfloat16> : StoreRow16<__nv_bfloat16> {};
 
-template <int BN, typename TM>
-__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_v,
-                                                               const __grid_constant__ CUtensorMap map_u,
-                                                               TM *__restrict__ m, int tiles, int c_pad, int k_out,
-                                                               int n_blocks, uint32_t idesc, int n_stages) {
-  using C = Cfg<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzled stages need 1024-byte alignment
-  uint8_t *ring_ptr = smem_raw + (ring - raw);
-  // The ring holds n_stages stages, no more than the reduction has slabs: a short reduction then leaves room for
-  // several CTAs per SM, whose load, MMA and store phases overlap each other.
-  const int ring_bytes = n_stages * C::STAGE_BYTES;
-  const uint32_t bars = ring + ring_bytes;    // full[n_stages], empty[n_stages], acc_full
-  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(ring_ptr + ring_bytes + 128);
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ring_ptr + ring_bytes + 132);
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (n_stages + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * n_stages);
+// What the operands are and how a product is formed.
+enum Kind : int { KIND_F16 = 0, KIND_TF32 = 1, KIND_TF32X3 = 2 };
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_blk = blockIdx.x % n_blocks, m_blk = blockIdx.x / n_blocks, pos = blockIdx.y;
-  const int n_kb = (c_pad + BK - 1) / BK;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < n_stages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    mbar_init(acc_bar, 1);
-    *abort_word = 0u;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {  // whole warp: allocate BN fp32 accumulator columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"((uint32_t)BN) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_acc = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < n_kb; ++kb) {
-        const int s = kb % n_stages;
-        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) break;
-        mbar_expect_tx(full_bar(s), (uint32_t)C::STAGE_BYTES);
-        const uint32_t a_dst = ring + s * C::STAGE_BYTES;
-        tma_load_3d(a_dst, &map_v, full_bar(s), kb * BK, m_blk * BM, pos);
-        tma_load_3d(a_dst + A_STAGE_BYTES, &map_u, full_bar(s), kb * BK, n_blk * BN, pos);
-        issued = kb + 1;
-      }
-      if (*abort_word != 0u) {
-        // Aborting: nobody may be consuming any more.  Wait (bounded) until every load this thread issued
-        // has landed, so no bulk copy is still writing shared memory when the CTA exits.
-        for (int kb = (issued > n_stages ? issued - n_stages : 0); kb < issued; ++kb) {
-          const long long start = clock64();
-          while (!mbar_try_wait(full_bar(kb % n_stages), (uint32_t)(kb / n_stages) & 1u)) {
-            if (clock64() - start > WAIT_LIMIT_CLOCKS) { atomicCAS(&g_device_error, 0u, (unsigned)ERR_DRAIN); break; }
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      bool ok = true;
-      for (int kb = 0; kb < n_kb && ok; ++kb) {
-        const int s = kb % n_stages;
-        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
-        ok = mbar_wait(full_bar(s), ph, abort_word, ERR_MMA_FULL);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_base = ring + s * C::STAGE_BYTES;
-        const uint64_t adesc = make_smem_desc(a_base);
-        const uint64_t bdesc = make_smem_desc(a_base + A_STAGE_BYTES);
-#pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // advancing 16 elements along the reduction = 32 bytes = 2 descriptor address units
-          umma_f16(tmem_acc, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(empty_bar(s));  // stage reusable once these MMAs have read it
-      }
-      umma_commit(acc_bar);         // accumulator complete (or whatever was issued, when aborting)
-    }
-  }
-  __syncwarp();
-
-  if (warp >= 2) {
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    unsigned got = 0;
-    if (lane == 0) got = mbar_wait(acc_bar, 0u, abort_word, ERR_EPI_ACC) ? 1u : 0u;
-    got = __shfl_sync(0xffffffffu, got, 0);
-    const bool healthy = got != 0u && *abort_word == 0u;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float *stage = reinterpret_cast<float *>(ring_ptr) + (warp - 2) * (32 * 36);
-    const long long row0 = (long long)m_blk * BM + q * 32;
-    const int rows_valid = (int)max(0LL, min(32LL, (long long)tiles - row0));
-    TM *m_rows = m + ((long long)pos * tiles + row0) * k_out + (long long)n_blk * BN;
-    const bool vec_ok = (k_out % 8) == 0;
-    if (healthy) {
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int cols_valid = min(32, k_out - (n_blk * BN + c0));
-        if (cols_valid <= 0) break;   // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<float4 *>(stage + lane * 36 + 4 * j) =
-              make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                          __uint_as_float(r[4 * j + 3]));
-        __syncwarp();
-        if (vec_ok) {
-#pragma unroll
-          for (int it = 0; it < 32 / StoreRow<TM>::ROWS_PER_ITER; ++it)
-            StoreRow<TM>::run(stage, lane, it, m_rows + c0, (long long)k_out, rows_valid, cols_valid);
-        } else {  // k_out not a multiple of 8: rows of M are not 16-byte aligned, store element-wise
-          for (int rr = 0; rr < rows_valid; ++rr)
-            if (lane < cols_valid) Elem<TM>::store(m_rows + (long long)rr * k_out + c0 + lane, stage[rr * 36 + lane]);
-        }
-        __syncwarp();
-      }
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
-  }
-}
-
-// ---- fp32 operands on the tensor cores: kind::tf32, plain or as three products of a hi / lo split -----------------
+// fp32 operands on the tensor cores: kind::tf32, plain or as three products of a hi / lo split.
 // A tf32 multiply keeps 10 mantissa bits of each operand, which is not enough for the 1e-3 bound of the fp32 path
 // (measured: see the cfg1 parity test).  Writing every operand as hi + lo, with hi the value rounded to tf32 and
 // lo = x - hi (exact in fp32), the three products hi*hi + lo*hi + hi*lo leave an error of order 2^-21.  The split
-// is made in shared memory: the epilogue warps, idle during the main loop, rewrite each stage in place as it lands
-// (hi over the loaded values, lo into a second copy at the same offsets, so the 128-byte swizzle carries over) and
-// then hand it to the MMA thread.  V, U and the transforms that produce them are untouched: no second pass over HBM.
-constexpr int BK32 = 32;     // fp32 elements per 128-byte swizzle row
-constexpr int UMMA_K32 = 8;  // reduction depth of one kind::tf32 MMA (32 bytes)
-
-template <int BN, bool SPLIT> struct Cfg32 {
-  static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
-  static constexpr int STAGE_BYTES = (SPLIT ? 2 : 1) * (A_BYTES + B_BYTES);   // [A hi | B hi | A lo | B lo]
-  static constexpr int STAGES = (BN == 256 ? 2 : (BN == 128 ? 3 : 4));
-  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = RING_BYTES + 1024 + 256;
-  static_assert(RING_BYTES >= 4 * 32 * 36 * 4, "epilogue staging must fit in the ring");
-  static_assert(SMEM_BYTES <= 227 * 1024, "stage ring exceeds shared memory");
-};
-
+// is made in shared memory: four warps rewrite each stage in place as it lands (hi over the loaded values, lo into a
+// second copy at the same offsets, so the 128-byte swizzle carries over) and then hand it to the MMA thread.  V, U
+// and the transforms that produce them are untouched: no second pass over HBM.
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -321,146 +170,210 @@ __device__ __forceinline__ float tf32_round(float x) {
   return __uint_as_float(r);
 }
 
-template <int BN, bool SPLIT>
-__global__ void __launch_bounds__(192, 1) gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_v,
-                                                            const __grid_constant__ CUtensorMap map_u,
-                                                            float *__restrict__ m, int tiles, int c_pad, int k_out,
-                                                            int n_blocks, uint32_t idesc, int n_stages) {
-  using C = Cfg32<BN, SPLIT>;
+constexpr int EPI_WARPS = 8;                                  // two per tensor-memory lane quarter: alternate 32-column chunks
+constexpr int EPI_STAGING_BYTES = EPI_WARPS * 32 * 36 * 4;   // per epilogue warp 32 rows x (32 + 4 pad) floats
+
+template <int BN, int KIND> struct PCfg {
+  static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;      // rows of one 128-byte swizzle atom: 64 halves or 32 floats
+  static constexpr int HALF_BYTES = A_BYTES + B_BYTES;              // what TMA loads per stage
+  static constexpr int STAGE_BYTES = (KIND == KIND_TF32X3 ? 2 : 1) * HALF_BYTES;   // [A hi | B hi | A lo | B lo]
+  static constexpr int FIXED_BYTES = EPI_STAGING_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  static constexpr int MAX_STAGES = 8;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS + (KIND == KIND_TF32X3 ? 128 : 0);
+  // CTAs that may share an SM: each holds 2 x BN of the 512 tensor-memory columns
+  static constexpr int TMEM_CTAS = 512 / (2 * BN);
+  static constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + FIXED_BYTES; }
+  // stages of a CTA that shares its SM with ctas - 1 others
+  static constexpr int stages_for(int ctas) {
+    int st = (227 * 1024 / ctas - FIXED_BYTES) / STAGE_BYTES;
+    return st > MAX_STAGES ? MAX_STAGES : st;
+  }
+};
+
+// Persistent: a few CTAs per SM walk the (position, row block, column block) work tiles with a fixed stride.  The TMA
+// ring runs on across tiles, and the accumulator is double-buffered in tensor memory (2 x BN columns), so the loads and
+// MMAs of the next tile overlap the epilogue of this one and the set-up (tensor-memory allocation, barrier
+// initialisation, descriptor fetch) is paid once per CTA instead of once per 128-row tile.  A short reduction runs
+// with a short ring and several CTAs per SM (as many as the tensor-memory columns allow): its time is the epilogue's
+// stores, and more epilogue warps per SM keep more of them in flight.
+template <int BN, typename TM, int KIND>
+__global__ void __launch_bounds__(PCfg<BN, KIND>::THREADS, 1)
+    gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_u,
+                           TM *__restrict__ m, int tiles, int c_pad, int k_out, int n_blocks, int m_blocks,
+                           long long total_work, uint32_t idesc, int n_stages) {
+  using C = PCfg<BN, KIND>;
+  const int NS = n_stages;
+  constexpr int BKE = KIND == KIND_F16 ? BK : 32;       // elements per 128-byte row of a stage
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t ring = (raw + 1023u) & ~1023u;
+  const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzled stages need 1024-byte alignment
   uint8_t *ring_ptr = smem_raw + (ring - raw);
-  // The ring holds n_stages stages, no more than the reduction has slabs: a short reduction then leaves room for
-  // several CTAs per SM, whose load, split, MMA and store phases overlap each other.
-  const int ring_bytes = n_stages * C::STAGE_BYTES;
-  const uint32_t bars = ring + ring_bytes;    // full[n_stages], empty[n_stages], split[n_stages], acc_full
-  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(ring_ptr + ring_bytes + 128);
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ring_ptr + ring_bytes + 132);
+  const int RING_BYTES = NS * C::STAGE_BYTES;
+  float *staging = reinterpret_cast<float *>(ring_ptr + RING_BYTES);
+  const uint32_t bars = ring + RING_BYTES + EPI_STAGING_BYTES;   // full[NS] empty[NS] split[NS] acc_full[2] acc_empty[2]
+  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(ring_ptr + RING_BYTES + EPI_STAGING_BYTES + 384);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ring_ptr + RING_BYTES + EPI_STAGING_BYTES + 388);
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (n_stages + s); };
-  auto split_bar = [&](int s) { return bars + 8u * (2 * n_stages + s); };
-  const uint32_t acc_bar = bars + 8u * (3 * n_stages);
+  auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
+  auto split_bar = [&](int s) { return bars + 8u * (2 * NS + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (3 * NS + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (3 * NS + 2 + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_blk = blockIdx.x % n_blocks, m_blk = blockIdx.x / n_blocks, pos = blockIdx.y;
-  const int n_kb = (c_pad + BK32 - 1) / BK32;
+  const int n_kb = (c_pad + BKE - 1) / BKE;
+  const long long w0 = blockIdx.x, w_step = gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < n_stages; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
       mbar_init(split_bar(s), 4);          // one arrival per splitting warp
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);           // the MMA thread's commit
+      mbar_init(acc_empty(b), EPI_WARPS);  // one arrival per epilogue warp
+    }
     *abort_word = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"((uint32_t)BN) : "memory");
+  if (warp == 1) {  // whole warp: two accumulators of BN fp32 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_acc = *tmem_slot;
-  constexpr int HALF_BYTES = C::A_BYTES + C::B_BYTES;     // the loaded (hi) half of a stage
+  const long long mn = (long long)m_blocks * n_blocks;
 
   if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < n_kb; ++kb) {
-        const int s = kb % n_stages;
-        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) break;
-        mbar_expect_tx(full_bar(s), (uint32_t)HALF_BYTES);
-        const uint32_t a_dst = ring + s * C::STAGE_BYTES;
-        tma_load_3d(a_dst, &map_v, full_bar(s), kb * BK32, m_blk * BM, pos);
-        tma_load_3d(a_dst + C::A_BYTES, &map_u, full_bar(s), kb * BK32, n_blk * BN, pos);
-        issued = kb + 1;
+      uint32_t it = 0, ph = 0;
+      int s = 0;
+      bool alive = true;
+      for (long long w = w0; w < total_work && alive; w += w_step) {
+        const int pos = (int)(w / mn);
+        const int rem = (int)(w - (long long)pos * mn);
+        const int m_blk = rem / n_blocks, n_blk = rem - m_blk * n_blocks;
+        for (int kb = 0; kb < n_kb; ++kb, ++it, (++s == NS ? (s = 0, ph ^= 1u) : 0u)) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) { alive = false; break; }
+          mbar_expect_tx(full_bar(s), (uint32_t)C::HALF_BYTES);
+          const uint32_t a_dst = ring + s * C::STAGE_BYTES;
+          tma_load_3d(a_dst, &map_v, full_bar(s), kb * BKE, m_blk * BM, pos);
+          tma_load_3d(a_dst + C::A_BYTES, &map_u, full_bar(s), kb * BKE, n_blk * BN, pos);
+        }
       }
-      if (*abort_word != 0u) {   // let every load issued land before the CTA exits
-        for (int kb = (issued > n_stages ? issued - n_stages : 0); kb < issued; ++kb) {
+      if (*abort_word != 0u) {
+        // Aborting: nobody may be consuming any more.  Wait (bounded) until every load this thread issued
+        // has landed, so no bulk copy is still writing shared memory when the CTA exits.
+        for (uint32_t j = (it > (uint32_t)NS ? it - (uint32_t)NS : 0u); j < it; ++j) {
           const long long start = clock64();
-          while (!mbar_try_wait(full_bar(kb % n_stages), (uint32_t)(kb / n_stages) & 1u)) {
+          while (!mbar_try_wait(full_bar((int)(j % (uint32_t)NS)), (j / (uint32_t)NS) & 1u)) {
             if (clock64() - start > WAIT_LIMIT_CLOCKS) { atomicCAS(&g_device_error, 0u, (unsigned)ERR_DRAIN); break; }
           }
         }
       }
     }
   } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      bool ok = true;
-      for (int kb = 0; kb < n_kb && ok; ++kb) {
-        const int s = kb % n_stages;
-        const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
-        ok = mbar_wait(SPLIT ? split_bar(s) : full_bar(s), ph, abort_word, ERR_MMA_FULL);
-        if (!ok) break;
+      uint32_t n_done = 0, ph = 0;
+      int s = 0;
+      bool alive = true;
+      for (long long w = w0; w < total_work && alive; w += w_step, ++n_done) {
+        const int buf = (int)(n_done & 1u);
+        if (!mbar_wait(acc_empty(buf), ((n_done >> 1) & 1u) ^ 1u, abort_word, ERR_EPI_ACC)) { alive = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_base = ring + s * C::STAGE_BYTES;
-        const uint64_t a_hi = make_smem_desc(a_base), b_hi = make_smem_desc(a_base + C::A_BYTES);
-        const uint64_t a_lo = make_smem_desc(a_base + HALF_BYTES), b_lo = make_smem_desc(a_base + HALF_BYTES + C::A_BYTES);
+        const uint32_t d = tmem_acc + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < n_kb; ++kb, (++s == NS ? (s = 0, ph ^= 1u) : 0u)) {
+          if (!mbar_wait(KIND == KIND_TF32X3 ? split_bar(s) : full_bar(s), ph, abort_word, ERR_MMA_FULL)) { alive = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_base = ring + s * C::STAGE_BYTES;
+          const uint64_t a_hi = make_smem_desc(a_base), b_hi = make_smem_desc(a_base + C::A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK32 / UMMA_K32; ++k) {   // 8 fp32 along the reduction = 32 bytes = 2 descriptor address units
-          if (SPLIT) {
-            umma_tf32(tmem_acc, a_lo + 2u * k, b_hi + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            umma_tf32(tmem_acc, a_hi + 2u * k, b_lo + 2u * k, idesc, 1u);
-            umma_tf32(tmem_acc, a_hi + 2u * k, b_hi + 2u * k, idesc, 1u);
-          } else {
-            umma_tf32(tmem_acc, a_hi + 2u * k, b_hi + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {   // 16 halves or 8 floats along the reduction = 32 bytes = 2 descriptor address units
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            if (KIND == KIND_F16) {
+              umma_f16(d, a_hi + 2u * k, b_hi + 2u * k, idesc, acc);
+            } else if (KIND == KIND_TF32) {
+              umma_tf32(d, a_hi + 2u * k, b_hi + 2u * k, idesc, acc);
+            } else {
+              const uint64_t a_lo = make_smem_desc(a_base + C::HALF_BYTES), b_lo = make_smem_desc(a_base + C::HALF_BYTES + C::A_BYTES);
+              umma_tf32(d, a_lo + 2u * k, b_hi + 2u * k, idesc, acc);
+              umma_tf32(d, a_hi + 2u * k, b_lo + 2u * k, idesc, 1u);
+              umma_tf32(d, a_hi + 2u * k, b_hi + 2u * k, idesc, 1u);
+            }
           }
+          umma_commit(empty_bar(s));  // stage reusable once these MMAs have read it
         }
-        umma_commit(empty_bar(s));
+        umma_commit(acc_full(buf));   // accumulator complete (or whatever was issued, when aborting)
       }
-      umma_commit(acc_bar);
     }
-  } else if (SPLIT) {
-    // warps 2..5: rewrite each landed stage as hi (in place) and lo (second half of the stage)
-    const int st = threadIdx.x - 64;      // 0..127
-    bool ok = true;
-    for (int kb = 0; kb < n_kb && ok; ++kb) {
-      const int s = kb % n_stages;
-      const uint32_t ph = (uint32_t)(kb / n_stages) & 1u;
-      unsigned got = 0;
-      if (lane == 0) got = mbar_wait(full_bar(s), ph, abort_word, ERR_MMA_FULL) ? 1u : 0u;
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (got == 0u) { ok = false; break; }
-      float4 *hi = reinterpret_cast<float4 *>(ring_ptr + s * C::STAGE_BYTES);
-      float4 *lo = reinterpret_cast<float4 *>(ring_ptr + s * C::STAGE_BYTES + HALF_BYTES);
+  } else if (warp >= 2 + EPI_WARPS) {
+    // ---------------------------------------------------------------- hi / lo split (three-product kind only)
+    const int st = threadIdx.x - (64 + 32 * EPI_WARPS);      // 0..127
+    uint32_t ph = 0;
+    int s = 0;
+    bool alive = true;
+    for (long long w = w0; w < total_work && alive; w += w_step) {
+      for (int kb = 0; kb < n_kb; ++kb, (++s == NS ? (s = 0, ph ^= 1u) : 0u)) {
+        unsigned got = 0;
+        if (lane == 0) got = mbar_wait(full_bar(s), ph, abort_word, ERR_MMA_FULL) ? 1u : 0u;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (got == 0u) { alive = false; break; }
+        float4 *hi = reinterpret_cast<float4 *>(ring_ptr + s * C::STAGE_BYTES);
+        float4 *lo = reinterpret_cast<float4 *>(ring_ptr + s * C::STAGE_BYTES + C::HALF_BYTES);
 #pragma unroll 4
-      for (int i = st; i < HALF_BYTES / 16; i += 128) {
-        const float4 x = hi[i];
-        float4 h, l;
-        h.x = tf32_round(x.x); h.y = tf32_round(x.y); h.z = tf32_round(x.z); h.w = tf32_round(x.w);
-        l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
-        hi[i] = h;
-        lo[i] = l;
+        for (int i = st; i < C::HALF_BYTES / 16; i += 128) {
+          const float4 x = hi[i];
+          float4 h, l;
+          h.x = tf32_round(x.x); h.y = tf32_round(x.y); h.z = tf32_round(x.z); h.w = tf32_round(x.w);
+          l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
+          hi[i] = h;
+          lo[i] = l;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these stores before the MMA's reads
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(split_bar(s)) : "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these stores before the MMA's reads
-      __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(split_bar(s)) : "memory");
     }
-  }
-  __syncwarp();
-
-  if (warp >= 2) {
-    const int q = warp & 3;
-    unsigned got = 0;
-    if (lane == 0) got = mbar_wait(acc_bar, 0u, abort_word, ERR_EPI_ACC) ? 1u : 0u;
-    got = __shfl_sync(0xffffffffu, got, 0);
-    const bool healthy = got != 0u && *abort_word == 0u;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float *stage = reinterpret_cast<float *>(ring_ptr) + (warp - 2) * (32 * 36);
-    const long long row0 = (long long)m_blk * BM + q * 32;
-    const int rows_valid = (int)max(0LL, min(32LL, (long long)tiles - row0));
-    float *m_rows = m + ((long long)pos * tiles + row0) * k_out + (long long)n_blk * BN;
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..9)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;   // which of the two warps of that quarter: even or odd 32-column chunks
+    float *stage = staging + (warp - 2) * (32 * 36);
     const bool vec_ok = (k_out % 8) == 0;
-    if (healthy) {
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int cols_valid = min(32, k_out - (n_blk * BN + c0));
-        if (cols_valid <= 0) break;
+    uint32_t n_done = 0;
+    bool alive = true;
+    for (long long w = w0; w < total_work && alive; w += w_step, ++n_done) {
+      const int pos = (int)(w / mn);
+      const int rem = (int)(w - (long long)pos * mn);
+      const int m_blk = rem / n_blocks, n_blk = rem - m_blk * n_blocks;
+      const int buf = (int)(n_done & 1u);
+      unsigned got = 0;
+      if (lane == 0) got = mbar_wait(acc_full(buf), (n_done >> 1) & 1u, abort_word, ERR_EPI_ACC) ? 1u : 0u;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got == 0u || *abort_word != 0u) { alive = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const long long row0 = (long long)m_blk * BM + q * 32;
+      const int rows_valid = (int)max(0LL, min(32LL, (long long)tiles - row0));
+      TM *m_rows = m + ((long long)pos * tiles + row0) * k_out + (long long)n_blk * BN;
+      const int cols_here = min(BN, k_out - n_blk * BN);            // >= 1
+      const int n_chunks = (cols_here + 31) / 32;
+      if (half >= n_chunks) {            // nothing to read for this warp: its share of the hand-back
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+      }
+      for (int ch = half; ch < n_chunks; ch += 2) {
+        const int c0 = ch * 32;
+        const int cols_valid = min(32, cols_here - c0);
         uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        if (ch + 2 >= n_chunks) {        // this warp's last columns are in registers: hand the accumulator back to the MMA thread
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<float4 *>(stage + lane * 36 + 4 * j) =
@@ -469,11 +382,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tf32_kernel(const __grid_constant
         __syncwarp();
         if (vec_ok) {
 #pragma unroll
-          for (int it = 0; it < 32 / StoreRow<float>::ROWS_PER_ITER; ++it)
-            StoreRow<float>::run(stage, lane, it, m_rows + c0, (long long)k_out, rows_valid, cols_valid);
-        } else {
+          for (int itr = 0; itr < 32 / StoreRow<TM>::ROWS_PER_ITER; ++itr)
+            StoreRow<TM>::run(stage, lane, itr, m_rows + c0, (long long)k_out, rows_valid, cols_valid);
+        } else {  // k_out not a multiple of 8: rows of M are not 16-byte aligned, store element-wise
           for (int rr = 0; rr < rows_valid; ++rr)
-            if (lane < cols_valid) m_rows[(long long)rr * k_out + c0 + lane] = stage[rr * 36 + lane];
+            if (lane < cols_valid) Elem<TM>::store(m_rows + (long long)rr * k_out + c0 + lane, stage[rr * 36 + lane]);
         }
         __syncwarp();
       }
@@ -483,7 +396,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tf32_kernel(const __grid_constant
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(2 * BN)) : "memory");
   }
 }
 
@@ -522,67 +435,76 @@ static bool make_operand_map(CUtensorMap *map, int dtype, const void *base, int 
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, typename TM>
+static int device_sm_count() {
+  static std::mutex mu;
+  static std::map<int, int> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  auto f = cache.find(dev);
+  if (f != cache.end()) return f->second;
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+  cache[dev] = n;
+  return n;
+}
+
+template <int BN, typename TM, int KIND>
 static cudaError_t run(int dtype, int positions, long long tiles, int c_pad, int k_out, const void *v, const void *u,
                        void *m, cudaStream_t s, const char **detail) {
-  using C = Cfg<BN>;
+  using C = PCfg<BN, KIND>;
   CUtensorMap map_v, map_u;
   if (!make_operand_map(&map_v, dtype, v, c_pad, tiles, positions, BM) ||
       !make_operand_map(&map_u, dtype, u, c_pad, k_out, positions, BN)) {
     *detail = "cuTensorMapEncodeTiled failed (operands must be 16-byte aligned, c_pad a multiple of 8)";
     return cudaErrorInvalidValue;
   }
-  auto kern = gemm_tcgen05_kernel<BN, TM>;
-  const int n_kb = (c_pad + BK - 1) / BK;
-  int n_stages = n_kb < C::STAGES ? n_kb : C::STAGES;
-  if (n_stages * C::STAGE_BYTES < 4 * 32 * 36 * 4) n_stages = C::STAGES;   // the epilogue stages its rows in the ring
-  const int smem_bytes = n_stages * C::STAGE_BYTES + 1024 + 256;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  auto kern = gemm_persistent_kernel<BN, TM, KIND>;
+  // CTAs per SM: one with a deep ring for a long reduction; two with short rings for a reduction of one or two slabs,
+  // whose time is the stores of M.  WINOCONV_GEMM_CTAS overrides (experiments; at most what the tensor memory allows).
+  const int n_kb = (c_pad + (KIND == KIND_F16 ? 64 : 32) - 1) / (KIND == KIND_F16 ? 64 : 32);
+  static const int ctas_env = [] { const char *v = getenv("WINOCONV_GEMM_CTAS"); return v && *v ? atoi(v) : 0; }();
+  int ctas = (n_kb <= 2 && C::TMEM_CTAS >= 2) ? 2 : 1;   // measured: a reduction of four slabs already wants the deep ring
+  if (ctas_env >= 1) ctas = ctas_env < C::TMEM_CTAS ? ctas_env : C::TMEM_CTAS;
+  while (ctas > 1 && C::stages_for(ctas) < 2) --ctas;
+  int n_stages = C::stages_for(ctas);
+  // a ring no deeper than two tiles' worth of slabs, but deep enough that no more CTAs fit an SM than planned
+  while (n_stages > 2 && n_stages > 2 * n_kb && C::smem_bytes(n_stages - 1) > 227 * 1024 / (ctas + 1)) --n_stages;
+  const int smem_bytes = C::smem_bytes(n_stages);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(C::stages_for(1)));
   if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
   const int n_blocks = (k_out + BN - 1) / BN;
   const long long m_blocks = (tiles + BM - 1) / BM;
   if (m_blocks * n_blocks > 0x7fffffffLL) { *detail = "too many tile blocks for one launch"; return cudaErrorInvalidConfiguration; }
-  // instruction descriptor: D = f32, A = B = f16 (0) or bf16 (1), both reduction-major, N >> 3, M >> 4
-  const uint32_t fmt = dtype == WINOCONV_F16 ? 0u : 1u;
+  const long long total = m_blocks * n_blocks * positions;
+  const int sms = device_sm_count();
+  if (sms <= 0) { *detail = "no device"; return cudaErrorNoDevice; }
+  // instruction descriptor: D = f32, A = B = f16 (0) / bf16 (1) / tf32 (2), both reduction-major, N >> 3, M >> 4
+  const uint32_t fmt = KIND != KIND_F16 ? 2u : (dtype == WINOCONV_F16 ? 0u : 1u);
   const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-  dim3 grid((unsigned)(m_blocks * n_blocks), (unsigned)positions), block(192);
-  kern<<<grid, block, smem_bytes, s>>>(map_v, map_u, (TM *)m, (int)tiles, c_pad, k_out, n_blocks, idesc, n_stages);
+  const long long slots = (long long)sms * ctas;
+  const unsigned grid = (unsigned)(total < slots ? total : slots);
+  kern<<<grid, C::THREADS, smem_bytes, s>>>(map_v, map_u, (TM *)m, (int)tiles, c_pad, k_out, n_blocks, (int)m_blocks, total, idesc, n_stages);
   return cudaGetLastError();
+}
+
+// Wider than 128 output channels: 256-wide blocks read V once per 256 channels, 128-wide blocks fill the last round of
+// the SMs better on a small problem; take whichever needs less time in whole rounds (a 256-wide block counts double).
+static bool prefer_bn128(int positions, long long tiles, int k_out) {
+  const int sms = device_sm_count();
+  if (sms <= 0) return false;
+  const long long m_blocks = (tiles + BM - 1) / BM;
+  const long long w256 = m_blocks * positions * ((k_out + 255) / 256), w128 = m_blocks * positions * ((k_out + 127) / 128);
+  return (w128 + sms - 1) / sms < 2 * ((w256 + sms - 1) / sms);
 }
 
 template <typename TM>
 static cudaError_t pick_bn(int dtype, int positions, long long tiles, int c_pad, int k_out, const void *v,
                            const void *u, void *m, cudaStream_t s, const char **detail) {
-  if (k_out <= 64) return run<64, TM>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
-  if (k_out <= 128) return run<128, TM>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
-  return run<256, TM>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
-}
-
-template <int BN, bool SPLIT>
-static cudaError_t run32(int positions, long long tiles, int c_pad, int k_out, const void *v, const void *u, void *m,
-                         cudaStream_t s, const char **detail) {
-  using C = Cfg32<BN, SPLIT>;
-  CUtensorMap map_v, map_u;
-  if (!make_operand_map(&map_v, WINOCONV_F32, v, c_pad, tiles, positions, BM) ||
-      !make_operand_map(&map_u, WINOCONV_F32, u, c_pad, k_out, positions, BN)) {
-    *detail = "cuTensorMapEncodeTiled failed (operands must be 16-byte aligned, c_pad a multiple of 8)";
-    return cudaErrorInvalidValue;
-  }
-  auto kern = gemm_tf32_kernel<BN, SPLIT>;
-  const int n_kb = (c_pad + BK32 - 1) / BK32;
-  int n_stages = n_kb < C::STAGES ? n_kb : C::STAGES;
-  if (n_stages * C::STAGE_BYTES < 4 * 32 * 36 * 4) n_stages = C::STAGES;   // the epilogue stages its rows in the ring
-  const int smem_bytes = n_stages * C::STAGE_BYTES + 1024 + 256;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-  if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
-  const int n_blocks = (k_out + BN - 1) / BN;
-  const long long m_blocks = (tiles + BM - 1) / BM;
-  if (m_blocks * n_blocks > 0x7fffffffLL) { *detail = "too many tile blocks for one launch"; return cudaErrorInvalidConfiguration; }
-  // instruction descriptor: D = f32, A = B = tf32 (2), both reduction-major, N >> 3, M >> 4
-  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-  dim3 grid((unsigned)(m_blocks * n_blocks), (unsigned)positions), block(192);
-  kern<<<grid, block, smem_bytes, s>>>(map_v, map_u, (float *)m, (int)tiles, c_pad, k_out, n_blocks, idesc, n_stages);
-  return cudaGetLastError();
+  if (k_out <= 64) return run<64, TM, KIND_F16>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  if (k_out <= 128 || prefer_bn128(positions, tiles, k_out))
+    return run<128, TM, KIND_F16>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  return run<256, TM, KIND_F16>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
 }
 
 }  // namespace tc
@@ -593,12 +515,13 @@ cudaError_t launch_gemm_tf32(int split, int positions, long long tiles, int c_pa
   if (positions <= 0 || tiles <= 0) return cudaSuccess;
   if (c_pad % 8 != 0 || positions > 65535 || tiles > 0x7fffffffLL) { *detail = "c_pad must be a multiple of 8; positions <= 65535"; return cudaErrorInvalidValue; }
   if (split) {   // the split stages are twice as large: 128 output channels per CTA at most
-    if (k_out <= 64) return tc::run32<64, true>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
-    return tc::run32<128, true>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
+    if (k_out <= 64) return tc::run<64, float, tc::KIND_TF32X3>(WINOCONV_F32, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+    return tc::run<128, float, tc::KIND_TF32X3>(WINOCONV_F32, positions, tiles, c_pad, k_out, v, u, m, s, detail);
   }
-  if (k_out <= 64) return tc::run32<64, false>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
-  if (k_out <= 128) return tc::run32<128, false>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
-  return tc::run32<256, false>(positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  if (k_out <= 64) return tc::run<64, float, tc::KIND_TF32>(WINOCONV_F32, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  if (k_out <= 128 || tc::prefer_bn128(positions, tiles, k_out))
+    return tc::run<128, float, tc::KIND_TF32>(WINOCONV_F32, positions, tiles, c_pad, k_out, v, u, m, s, detail);
+  return tc::run<256, float, tc::KIND_TF32>(WINOCONV_F32, positions, tiles, c_pad, k_out, v, u, m, s, detail);
 }
 
 cudaError_t read_and_clear_device_error(cudaStream_t s, unsigned int *code) {

@@ -47,12 +47,15 @@ template <> struct ModeM<3> { static constexpr int MD = 1, MH = 6, MW = 6; };
 
 struct TileCoord { int n, td, th, tw; };
 
-__device__ __forceinline__ TileCoord decode_tile(const Geom &g, long long t) {
+// Tile indices fit 32 bits (2^31 tiles would be more outputs than the device holds): unsigned 32-bit divisions, a
+// fraction of the instructions of 64-bit ones -- the index arithmetic, not the transform, was most of these kernels.
+__device__ __forceinline__ TileCoord decode_tile(const Geom &g, long long t64) {
+  unsigned t = (unsigned)t64;
   TileCoord tc;
-  tc.tw = (int)(t % g.nW); t /= g.nW;
-  tc.th = (int)(t % g.nH); t /= g.nH;
-  tc.td = (int)(t % g.nD); t /= g.nD;
-  tc.n = (int)t;
+  unsigned q = t / (unsigned)g.nW; tc.tw = (int)(t - q * (unsigned)g.nW); t = q;
+  q = t / (unsigned)g.nH; tc.th = (int)(t - q * (unsigned)g.nH); t = q;
+  q = t / (unsigned)g.nD; tc.td = (int)(t - q * (unsigned)g.nD);
+  tc.n = (int)q;
   return tc;
 }
 
@@ -70,19 +73,26 @@ __device__ __forceinline__ void input_piece(const T *__restrict__ x, T *__restri
   const int zd = g.sD * (MD * tc.td + pc.start[0]) + pc.phase[0] - g.pD;
   const int zh = g.sH * (MH * tc.th + pc.start[1]) + pc.phase[1] - g.pH;
   const int zw = g.sW * (MW * tc.tw + pc.start[2]) + pc.phase[2] - g.pW;
+  // one 64-bit base per image, 32-bit pixel indices inside it, validity per row and per column
+  const T *xb = x + (long long)tc.n * g.D * g.H * g.W * g.C + c0;
+  bool okw[AW];
+  int iwv[AW];
+#pragma unroll
+  for (int k = 0; k < AW; ++k) { iwv[k] = zw + g.sW * k; okw[k] = (unsigned)iwv[k] < (unsigned)g.W; }
 #pragma unroll
   for (int i = 0; i < AD; ++i) {
     const int id = zd + g.sD * i;
+    const bool okd = (unsigned)id < (unsigned)g.D;
 #pragma unroll
     for (int j = 0; j < AH; ++j) {
       const int ih = zh + g.sH * j;
+      const bool okr = okd && (unsigned)ih < (unsigned)g.H;
+      const int rowpix = (id * g.H + ih) * g.W;
 #pragma unroll
       for (int k = 0; k < AW; ++k) {
-        const int iw = zw + g.sW * k;
         float(&dst)[VEC] = *reinterpret_cast<float(*)[VEC]>(&p[((i * AH + j) * AW + k) * VEC]);
-        if ((unsigned)id < (unsigned)g.D && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W) {
-          const long long off = ((((long long)tc.n * g.D + id) * g.H + ih) * g.W + iw) * g.C + c0;
-          VecIO<T, VEC>::load(x + off, dst);
+        if (okr && okw[k]) {
+          VecIO<T, VEC>::load(xb + (long long)(rowpix + iwv[k]) * g.C, dst);
         } else {
 #pragma unroll
           for (int l = 0; l < VEC; ++l) dst[l] = 0.f;
@@ -115,11 +125,12 @@ __global__ void __launch_bounds__(256) input_transform_kernel(const T *__restric
                                                               const __grid_constant__ Geom g, long long t0,
                                                               int n_tiles) {
   constexpr int MD = ModeM<MODE>::MD, MH = ModeM<MODE>::MH, MW = ModeM<MODE>::MW;
-  const int cvs = g.Cp / VEC;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = idx / cvs;
-  if (row >= n_tiles) return;
-  const int c0 = (int)(idx % cvs) * VEC;
+  const unsigned cvs = (unsigned)(g.Cp / VEC);
+  const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;      // tiles x channel vectors of a pass fit 32 bits
+  const unsigned row_u = idx / cvs;
+  if (row_u >= (unsigned)n_tiles) return;
+  const long long row = row_u;
+  const int c0 = (int)(idx - row_u * cvs) * VEC;
   const Piece &pc = g.pieces[blockIdx.y];
   const long long v_pos_stride = (long long)n_tiles * g.Cp;
   if (c0 >= g.C) {  // padding channels of V are zero so the GEMM can run over c_pad
@@ -258,11 +269,12 @@ __global__ void __launch_bounds__(256) output_transform_kernel(const TM *__restr
                                                                const __grid_constant__ Geom g, long long t0,
                                                                int n_tiles) {
   constexpr int MD = ModeM<MODE>::MD, MH = ModeM<MODE>::MH, MW = ModeM<MODE>::MW;
-  const int kvs = g.K / VEC;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = idx / kvs;
-  if (row >= n_tiles) return;
-  const int k0 = (int)(idx % kvs) * VEC;
+  const unsigned kvs = (unsigned)(g.K / VEC);
+  const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;      // tiles x channel vectors of a pass fit 32 bits
+  const unsigned row_u = idx / kvs;
+  if (row_u >= (unsigned)n_tiles) return;
+  const long long row = row_u;
+  const int k0 = (int)(idx - row_u * kvs) * VEC;
   const long long m_pos_stride = (long long)n_tiles * g.K;
   float acc[MD * MH * MW * VEC];
 #pragma unroll
@@ -338,6 +350,11 @@ __global__ void __launch_bounds__(256) output_transform_kernel(const TM *__restr
 // ------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------
+// The transform kernels index threads, tiles and the pixels of one image with 32 bits.
+static inline bool fits_32bit_indexing(const Geom &g, long long n_threads) {
+  return n_threads + 256 < (1LL << 32) && g.T < (1LL << 31) && (long long)g.D * g.H * g.W < (1LL << 31);
+}
+
 static inline int mode_of(const Geom &g) { return g.mH == 6 ? 3 : (g.mH == 4 ? 2 : (g.mD == 2 ? 1 : 0)); }
 
 // F(6x6,3x3) is instantiated for fp32 only (the planner refuses it for 16-bit operands)
@@ -372,6 +389,7 @@ cudaError_t launch_filter_transform(const Geom &g, int dtype, const void *w, voi
 template <typename T>
 static cudaError_t launch_input_v4_2d(const Geom &g, const void *x, void *v, long long t0, int n_tiles, cudaStream_t s) {
   const long long n = (long long)n_tiles * (g.Cp / 4);
+  if (!fits_32bit_indexing(g, n)) return cudaErrorInvalidValue;
   dim3 grid((unsigned)((n + 255) / 256), g.n_pieces), block(256);
   input_transform_kernel<T, 4, 0><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles);
   return cudaGetLastError();
@@ -380,6 +398,7 @@ static cudaError_t launch_input_v4_2d(const Geom &g, const void *x, void *v, lon
 template <typename T, int VEC>
 static cudaError_t launch_input_tv(const Geom &g, const void *x, void *v, long long t0, int n_tiles, cudaStream_t s) {
   const long long n = (long long)n_tiles * (g.Cp / VEC);
+  if (!fits_32bit_indexing(g, n)) return cudaErrorInvalidValue;
   dim3 grid((unsigned)((n + 255) / 256), g.n_pieces), block(256);
   switch (mode_of(g)) {
     case 0: input_transform_kernel<T, VEC, 0><<<grid, block, 0, s>>>((const T *)x, (T *)v, g, t0, n_tiles); break;
@@ -419,6 +438,7 @@ template <typename T, typename TM, int VEC>
 static cudaError_t launch_output_tv(const Geom &g, const void *m, void *y, const void *bias, long long t0, int n_tiles,
                                     cudaStream_t s) {
   const long long n = (long long)n_tiles * (g.K / VEC);
+  if (!fits_32bit_indexing(g, n)) return cudaErrorInvalidValue;
   dim3 grid((unsigned)((n + 255) / 256)), block(256);
   switch (mode_of(g)) {
     case 0:
@@ -445,6 +465,7 @@ static cudaError_t launch_output_t(const Geom &g, const void *m, void *y, const 
                                    cudaStream_t s) {
   if (mode_of(g) == 0 && g.K % 4 == 0) {   // 2-D F(2,r): four channels per thread
     const long long n = (long long)n_tiles * (g.K / 4);
+    if (!fits_32bit_indexing(g, n)) return cudaErrorInvalidValue;
     dim3 grid((unsigned)((n + 255) / 256)), block(256);
     output_transform_kernel<T, TM, 4, 0><<<grid, block, 0, s>>>((const TM *)m, (T *)y, (const T *)bias, g, t0, n_tiles);
     return cudaGetLastError();

@@ -269,6 +269,7 @@ def test_f63_fp32(n, c, k, sp, pad, eng):
     y, conv = run_engine(x, w, padding=pad, tile_m=6, gemm_engine=eng)
     assert conv.info.algo == capi.ALGO_STAGED and conv.info.positions == 64 and list(conv.info.tile_m) == [1, 6, 6]
     err = check_against_oracle(x, w, y, padding=pad)
+    print("F(6x6,3x3)", (n, c, k, sp), "engine", eng, err)
     assert err["E_B"] <= 2e-4, err       # measured 1e-5-class; well inside the 1e-3 contract
 
 
