@@ -6,7 +6,7 @@ legs of ``bench.py`` as the checker and as the timed CPU restatement of the refe
 
 Two things live here:
 
-1. The float64 direct-convolution oracle every result is judged against -- the same judge the
+1. The float64 direct-convolution oracle every result is compared with -- the same yardstick the
    reference uses in its own print-only checks (``example.py:104,115``: ``F.conv2d`` /
    ``F.conv3d`` on ``.double()`` tensors).  ``direct_conv_numpy`` is an independent sliding
    window restatement used to cross-check torch on small cases.
