@@ -169,6 +169,37 @@ template <> struct VecIO<__nv_bfloat16, 4> {
 // ------------------------------------------------------------------------------------------
 template <int M, int R> struct Xf;
 
+// Packed fp32 pairs (sm_100 executes add / mul / fma on two fp32 values per instruction): two channels of a tile move
+// through a transform as one 64-bit value, with the same roundings as the scalar form.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 template <> struct Xf<1, 1> {
   static constexpr int ALPHA = 1;
   template <int S> static __device__ __forceinline__ void bt(float *) {}
@@ -245,6 +276,22 @@ template <> struct Xf<4, 3> {
     d[3 * S] = eb + ob;
     d[4 * S] = eb - ob;
     d[5 * S] = fmaf(A2 * B2, d1, fmaf(-(A2 + B2), d3, d5));
+  }
+  // the same on two channels at once (S counts 64-bit elements); operation for operation the scalar form
+  template <int S> static __device__ __forceinline__ void bt2(uint64_t *d) {
+    const uint64_t nb2 = f2_pack(-B2, -B2), na2 = f2_pack(-A2, -A2), pa = f2_pack(PA, PA), pb = f2_pack(PB, PB);
+    const uint64_t a2b2 = f2_pack(A2 * B2, A2 * B2), nsum = f2_pack(-(A2 + B2), -(A2 + B2));
+    const uint64_t d0 = d[0], d1 = d[S], d2 = d[2 * S], d3 = d[3 * S], d4 = d[4 * S], d5 = d[5 * S];
+    const uint64_t ea = f2_fma(nb2, d2, d4);
+    const uint64_t oa = f2_mul(pa, f2_fma(nb2, d1, d3));
+    const uint64_t eb = f2_fma(na2, d2, d4);
+    const uint64_t ob = f2_mul(pb, f2_fma(na2, d1, d3));
+    d[0] = f2_fma(a2b2, d0, f2_fma(nsum, d2, d4));
+    d[S] = f2_add(ea, oa);
+    d[2 * S] = f2_sub(ea, oa);
+    d[3 * S] = f2_add(eb, ob);
+    d[4 * S] = f2_sub(eb, ob);
+    d[5 * S] = f2_fma(a2b2, d1, f2_fma(nsum, d3, d5));
   }
   template <int SI, int SO> static __device__ __forceinline__ void g(const float *w, float *u) {
     constexpr float F0 = 1.f / (A2 * B2), FA = 1.f / (2.f * A2 * (A2 - B2)), FB = 1.f / (2.f * B2 * (B2 - A2));

@@ -76,9 +76,13 @@ __device__ __forceinline__ void input_piece(const T *__restrict__ x, T *__restri
   // one 64-bit base per image, 32-bit pixel indices inside it, validity per row and per column
   const T *xb = x + (long long)tc.n * g.D * g.H * g.W * g.C + c0;
   bool okw[AW];
-  int iwv[AW];
+  int colofs[AW];      // element offset of a patch column within its image row
 #pragma unroll
-  for (int k = 0; k < AW; ++k) { iwv[k] = zw + g.sW * k; okw[k] = (unsigned)iwv[k] < (unsigned)g.W; }
+  for (int k = 0; k < AW; ++k) {
+    const int iw = zw + g.sW * k;
+    okw[k] = (unsigned)iw < (unsigned)g.W;
+    colofs[k] = iw * g.C;
+  }
 #pragma unroll
   for (int i = 0; i < AD; ++i) {
     const int id = zd + g.sD * i;
@@ -87,12 +91,12 @@ __device__ __forceinline__ void input_piece(const T *__restrict__ x, T *__restri
     for (int j = 0; j < AH; ++j) {
       const int ih = zh + g.sH * j;
       const bool okr = okd && (unsigned)ih < (unsigned)g.H;
-      const int rowpix = (id * g.H + ih) * g.W;
+      const T *rowp = xb + (long long)((id * g.H + ih) * g.W) * g.C;      // one 64-bit product per patch row
 #pragma unroll
       for (int k = 0; k < AW; ++k) {
         float(&dst)[VEC] = *reinterpret_cast<float(*)[VEC]>(&p[((i * AH + j) * AW + k) * VEC]);
         if (okr && okw[k]) {
-          VecIO<T, VEC>::load(xb + (long long)(rowpix + iwv[k]) * g.C, dst);
+          VecIO<T, VEC>::load(rowp + colofs[k], dst);
         } else {
 #pragma unroll
           for (int l = 0; l < VEC; ++l) dst[l] = 0.f;
@@ -100,6 +104,24 @@ __device__ __forceinline__ void input_piece(const T *__restrict__ x, T *__restri
       }
     }
   }
+  if constexpr (VEC == 2 && MD == 1 && MH == 4 && MW == 4 && RH == 3 && RW == 3) {
+    // F(4x4,3x3) over a channel pair: both passes on packed fp32 pairs (half the arithmetic instructions, same roundings)
+    uint64_t q[AH * AW];
+#pragma unroll
+    for (int i = 0; i < AH * AW; ++i) q[i] = f2_pack(p[2 * i], p[2 * i + 1]);
+#pragma unroll
+    for (int i = 0; i < AH; ++i) XW::template bt2<1>(&q[i * AW]);
+#pragma unroll
+    for (int k = 0; k < AW; ++k) XH::template bt2<AW>(&q[k]);
+    T *dstq = v + (long long)pc.pos_base * v_pos_stride + v_row * g.Cp + c0;
+#pragma unroll
+    for (int i = 0; i < AH * AW; ++i) {   // a running pointer: one 64-bit add per position, no 64-bit product
+      float o[2];
+      f2_unpack(q[i], o[0], o[1]);
+      VecIO<T, 2>::store(dstq, o);
+      dstq += v_pos_stride;
+    }
+  } else {
   // along W (stride VEC), H (stride AW*VEC), D (stride AH*AW*VEC)
 #pragma unroll
   for (int i = 0; i < AD * AH; ++i)
@@ -116,8 +138,10 @@ __device__ __forceinline__ void input_piece(const T *__restrict__ x, T *__restri
 #pragma unroll
   for (int q = 0; q < AD * AH * AW; ++q) {
     float(&src)[VEC] = *reinterpret_cast<float(*)[VEC]>(&p[q * VEC]);
-    VecIO<T, VEC>::store(dst + (long long)q * v_pos_stride, src);
+    VecIO<T, VEC>::store(dst, src);
+    dst += v_pos_stride;
   }
+  }   // generic path
 }
 
 template <typename T, int VEC, int MODE>
@@ -243,7 +267,8 @@ __device__ __forceinline__ void output_piece(const TM *__restrict__ m, float *ac
 #pragma unroll
     for (int k = 0; k < AW; ++k) {
       float(&dst)[VEC] = *reinterpret_cast<float(*)[VEC]>(&row[k * VEC]);
-      VecIO<TM, VEC>::load(src + (long long)(i * AW + k) * m_pos_stride, dst);
+      VecIO<TM, VEC>::load(src, dst);
+      src += m_pos_stride;      // positions are consecutive: a running pointer instead of a 64-bit product per load
     }
 #pragma unroll
     for (int l = 0; l < VEC; ++l) XW::template at<VEC, VEC>(&row[l], &t1[i * MW * VEC + l]);
