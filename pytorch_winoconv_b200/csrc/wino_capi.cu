@@ -461,7 +461,16 @@ static int forward_impl(const winoconv_desc_t *desc, const void *x, const void *
   for (long long t0 = 0; t0 < g.T && result == WINOCONV_OK; t0 += block) {
     const int n = (int)std::min<long long>(block, g.T - t0);
     cudaError_t e = mark();
-    if (e == cudaSuccess) e = launch_input_transform(g, plan.dtype, x, v_ws, t0, n, s);
+    if (e == cudaSuccess) {
+      static const int xt_env = [] { const char *v = getenv("WINOCONV_XF_TMA"); return v && *v ? atoi(v) : 1; }();
+      if (xt_env != 0 && input_f43_tma_applies(g, plan.dtype, x, t0, n)) {
+        const char *detail = "";
+        e = launch_input_f43_tma(g, plan.dtype, x, v_ws, s, &detail);
+        if (e != cudaSuccess) { result = cuda_fail(e, detail && *detail ? detail : "input transform launch"); break; }
+      } else {
+        e = launch_input_transform(g, plan.dtype, x, v_ws, t0, n, s);
+      }
+    }
     if (e != cudaSuccess) { result = cuda_fail(e, "input transform launch"); break; }
     if ((e = mark()) != cudaSuccess) { result = cuda_fail(e, "event record"); break; }
     result = run_gemm(plan.dtype, plan.product_dtype, plan.engine, g.positions, n, g.Cp, g.K, v_ws, u, m_ws, s);

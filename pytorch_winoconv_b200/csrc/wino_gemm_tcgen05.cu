@@ -400,6 +400,133 @@ __global__ void __launch_bounds__(PCfg<BN, KIND>::THREADS, 1)
   }
 }
 
+// ---- F(4x4,3x3) input transform with the raw patches staged through shared memory by TMA ---------------------------
+// V[pos][tile][c] = (B^T d B)[pos] for 16-bit layers whose channel count is a multiple of eight.  A persistent CTA walks
+// blocks of 4 x 8 tiles x 64 channels: one warp loads the block's 18 x 34-pixel patch with one 4-D
+// cp.async.bulk.tensor per block (out-of-bounds zero fill = the layer's padding) into a two-deep ring, twelve warps
+// transform it -- a warp takes one tile at a time, its lanes the 32 channel pairs of the block, so the shared-memory
+// reads are conflict-free and every store is a whole 128-byte line of V -- on packed fp32 pairs.  The global loads, whose
+// latency bound the one-thread-per-tile kernel, are the TMA engine's; the warps only compute and store.
+constexpr int XT_TH = 4, XT_TW = 8;                              // tiles per block
+constexpr int XT_PH = 4 * XT_TH + 2, XT_PW = 4 * XT_TW + 2;     // pixels per patch: 18 x 34
+constexpr int XT_C = 64;                                         // channels per patch: 128 bytes per pixel
+constexpr int XT_PATCH_BYTES = XT_PH * XT_PW * XT_C * 2;
+constexpr int XT_BUFS = 2;
+constexpr int XT_SMEM_BYTES = XT_BUFS * XT_PATCH_BYTES + 1024 + 256;
+constexpr int XT_WARPS = 12;                                     // transforming warps
+constexpr int XT_THREADS = 32 + 32 * XT_WARPS;
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+struct XtGeom {
+  int N, C, Cp, nH, nW, pH, pW;
+  int n_rb, n_cb, n_chb;      // blocks of tile rows, tile columns and channels
+  long long T, n_items;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(XT_THREADS, 1) input_f43_tma_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                       T *__restrict__ v, const __grid_constant__ XtGeom g) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 127u) & ~127u;
+  const uint8_t *base_ptr = smem_raw + (base - raw);
+  const uint32_t bars = base + XT_BUFS * XT_PATCH_BYTES;   // full[2] empty[2]
+  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(const_cast<uint8_t *>(base_ptr) + XT_BUFS * XT_PATCH_BYTES + 64);
+  auto full_bar = [&](int b) { return bars + 8u * b; };
+  auto empty_bar = [&](int b) { return bars + 8u * (XT_BUFS + b); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < XT_BUFS; ++b) {
+      mbar_init(full_bar(b), 1);
+      mbar_init(empty_bar(b), XT_WARPS);   // one arrival per transforming warp
+    }
+    *abort_word = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const long long per_img = (long long)g.n_rb * g.n_cb * g.n_chb;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (long long w = blockIdx.x; w < g.n_items; w += gridDim.x, ++it) {
+        const int b = (int)(it & 1u);
+        if (!mbar_wait(empty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) break;
+        const int n = (int)(w / per_img);
+        int rem = (int)(w - (long long)n * per_img);
+        const int chb = rem % g.n_chb; rem /= g.n_chb;
+        const int cb = rem % g.n_cb, rb = rem / g.n_cb;
+        mbar_expect_tx(full_bar(b), (uint32_t)XT_PATCH_BYTES);
+        tma_load_4d(base + b * XT_PATCH_BYTES, &map_x, full_bar(b), chb * XT_C, cb * (4 * XT_TW) - g.pW, rb * (4 * XT_TH) - g.pH, n);
+      }
+      if (*abort_word != 0u) {   // let the loads still in flight land before the shared memory goes away
+        for (uint32_t j = (it > 2u ? it - 2u : 0u); j < it; ++j) {
+          const long long start = clock64();
+          while (!mbar_try_wait(full_bar((int)(j & 1u)), (j >> 1) & 1u)) {
+            if (clock64() - start > WAIT_LIMIT_CLOCKS) { atomicCAS(&g_device_error, 0u, (unsigned)ERR_DRAIN); break; }
+          }
+        }
+      }
+    }
+  } else {
+    const int wi = warp - 1;               // 0..XT_WARPS-1: the block's tiles are dealt to the warps in turn
+    const long long v_pos_stride = g.T * g.Cp;
+    uint32_t it = 0;
+    bool alive = true;
+    for (long long w = blockIdx.x; w < g.n_items && alive; w += gridDim.x, ++it) {
+      const int b = (int)(it & 1u);
+      unsigned got = 0;
+      if (lane == 0) got = mbar_wait(full_bar(b), (it >> 1) & 1u, abort_word, ERR_MMA_FULL) ? 1u : 0u;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got == 0u) { alive = false; break; }
+      const int n = (int)(w / per_img);
+      int rem = (int)(w - (long long)n * per_img);
+      const int chb = rem % g.n_chb; rem /= g.n_chb;
+      const int cb = rem % g.n_cb, rb = rem / g.n_cb;
+      const int c = chb * XT_C + 2 * lane;             // this lane's channel pair
+      const uint8_t *patch = base_ptr + b * XT_PATCH_BYTES + lane * 4;
+      const int vh = min(XT_TH, g.nH - rb * XT_TH), vw = min(XT_TW, g.nW - cb * XT_TW);   // tiles of the block inside the image
+      if (c < g.Cp) {
+#pragma unroll 1
+        for (int t = wi; t < vh * vw; t += XT_WARPS) {
+          const int tr = t / vw, tw_warp = t - tr * vw;
+          const int th = rb * XT_TH + tr, tw = cb * XT_TW + tw_warp;
+          uint64_t q[36];
+#pragma unroll
+          for (int r = 0; r < 6; ++r)
+#pragma unroll
+            for (int sx = 0; sx < 6; ++sx) {
+              const uint32_t raw2 = *reinterpret_cast<const uint32_t *>(patch + ((4 * tr + r) * XT_PW + 4 * tw_warp + sx) * (XT_C * 2));
+              float f[2];
+              VecIO<T, 2>::load(reinterpret_cast<const T *>(&raw2), f);
+              q[r * 6 + sx] = f2_pack(f[0], f[1]);
+            }
+#pragma unroll
+          for (int r = 0; r < 6; ++r) Xf<4, 3>::template bt2<1>(&q[r * 6]);
+#pragma unroll
+          for (int sx = 0; sx < 6; ++sx) Xf<4, 3>::template bt2<6>(&q[sx]);
+          T *dst = v + (((long long)n * g.nH + th) * g.nW + tw) * g.Cp + c;
+#pragma unroll
+          for (int i = 0; i < 36; ++i) {
+            float o[2];
+            f2_unpack(q[i], o[0], o[1]);
+            VecIO<T, 2>::store(dst, o);
+            dst += v_pos_stride;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(b)) : "memory");
+    }
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -507,7 +634,49 @@ static cudaError_t pick_bn(int dtype, int positions, long long tiles, int c_pad,
   return run<256, TM, KIND_F16>(dtype, positions, tiles, c_pad, k_out, v, u, m, s, detail);
 }
 
+template <typename T>
+static cudaError_t run_input_f43_tma(const Geom &g, int dtype, const void *x, void *v, cudaStream_t s, const char **detail) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { *detail = "cuTensorMapEncodeTiled unavailable"; return cudaErrorNotSupported; }
+  CUtensorMap map_x;
+  const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
+  const cuuint64_t st[3] = {(cuuint64_t)g.C * 2ull, (cuuint64_t)g.C * 2ull * g.W, (cuuint64_t)g.C * 2ull * g.W * g.H};
+  const cuuint32_t box[4] = {(cuuint32_t)XT_C, (cuuint32_t)XT_PW, (cuuint32_t)XT_PH, 1u};
+  const cuuint32_t es[4] = {1u, 1u, 1u, 1u};
+  const CUtensorMapDataType dt = dtype == WINOCONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (enc(&map_x, dt, 4, const_cast<void *>(x), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    *detail = "cuTensorMapEncodeTiled failed for the input of the F(4x4,3x3) transform";
+    return cudaErrorInvalidValue;
+  }
+  XtGeom q;
+  q.N = g.N; q.C = g.C; q.Cp = g.Cp; q.nH = g.nH; q.nW = g.nW; q.pH = g.pH; q.pW = g.pW;
+  q.n_rb = (g.nH + XT_TH - 1) / XT_TH; q.n_cb = (g.nW + XT_TW - 1) / XT_TW; q.n_chb = (g.Cp + XT_C - 1) / XT_C;
+  q.T = g.T; q.n_items = (long long)g.N * q.n_rb * q.n_cb * q.n_chb;
+  auto kern = input_f43_tma_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, XT_SMEM_BYTES);
+  if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
+  const int sms = device_sm_count();
+  if (sms <= 0) { *detail = "no device"; return cudaErrorNoDevice; }
+  const unsigned grid = (unsigned)(q.n_items < sms ? q.n_items : sms);
+  kern<<<grid, XT_THREADS, XT_SMEM_BYTES, s>>>(map_x, (T *)v, q);
+  return cudaGetLastError();
+}
+
 }  // namespace tc
+
+bool input_f43_tma_applies(const Geom &g, int dtype, const void *x, long long t0, long long n_tiles) {
+  return (dtype == WINOCONV_F16 || dtype == WINOCONV_BF16) && g.mD == 1 && g.mH == 4 && g.mW == 4 && g.n_pieces == 1 &&
+         g.D == 1 && g.C % 8 == 0 && g.C == g.Cp && t0 == 0 && n_tiles == g.T && g.T < (1LL << 31) &&
+         (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+}
+
+cudaError_t launch_input_f43_tma(const Geom &g, int dtype, const void *x, void *v, cudaStream_t s, const char **detail) {
+  *detail = "";
+  if (dtype == WINOCONV_F16) return tc::run_input_f43_tma<__half>(g, dtype, x, v, s, detail);
+  return tc::run_input_f43_tma<__nv_bfloat16>(g, dtype, x, v, s, detail);
+}
+
 
 cudaError_t launch_gemm_tf32(int split, int positions, long long tiles, int c_pad, int k_out, const void *v,
                              const void *u, void *m, cudaStream_t s, const char **detail) {

@@ -30,6 +30,11 @@ cudaError_t launch_gemm_tcgen05(int dtype, int product_dtype, int positions, lon
 cudaError_t launch_gemm_tf32(int split, int positions, long long tiles, int c_pad, int k_out, const void *v,
                              const void *u, void *m, cudaStream_t s, const char **detail);
 
+// F(4x4,3x3) input transform of a whole 16-bit layer with the raw patches staged through shared memory by TMA
+// (channels a multiple of eight, one pass over all tiles); `applies` says whether a call qualifies.
+bool input_f43_tma_applies(const Geom &g, int dtype, const void *x, long long t0, long long n_tiles);
+cudaError_t launch_input_f43_tma(const Geom &g, int dtype, const void *x, void *v, cudaStream_t s, const char **detail);
+
 // Fused F(2x2,3x3) path (f16 / bf16): transformed filter u [16][K][R], then one kernel for the whole layer.
 cudaError_t launch_fused_filter_transform(const FGeom &g, int dtype, const void *w, void *u, cudaStream_t s);
 cudaError_t launch_fused_forward(const FGeom &g, int dtype, const void *x, const void *u, const void *bias, void *y,
