@@ -476,7 +476,16 @@ static int forward_impl(const winoconv_desc_t *desc, const void *x, const void *
     result = run_gemm(plan.dtype, plan.product_dtype, plan.engine, g.positions, n, g.Cp, g.K, v_ws, u, m_ws, s);
     if (result != WINOCONV_OK) break;
     if ((e = mark()) != cudaSuccess) { result = cuda_fail(e, "event record"); break; }
-    e = launch_output_transform(g, plan.dtype, plan.product_dtype, m_ws, y, bias, t0, n, s);
+    {
+      static const int yt_env = [] { const char *v = getenv("WINOCONV_XF_TMA"); return v && *v ? atoi(v) : 1; }();
+      if (yt_env != 0 && output_f43_tma_applies(g, plan.dtype, plan.product_dtype, m_ws, t0, n)) {
+        const char *detail = "";
+        e = launch_output_f43_tma(g, plan.dtype, plan.product_dtype, m_ws, y, bias, s, &detail);
+        if (e != cudaSuccess) { result = cuda_fail(e, detail && *detail ? detail : "output transform launch"); break; }
+      } else {
+        e = launch_output_transform(g, plan.dtype, plan.product_dtype, m_ws, y, bias, t0, n, s);
+      }
+    }
     if (e != cudaSuccess) { result = cuda_fail(e, "output transform launch"); break; }
     if ((e = mark()) != cudaSuccess) { result = cuda_fail(e, "event record"); break; }
     n_launch += 3;

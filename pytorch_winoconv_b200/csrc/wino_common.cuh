@@ -313,6 +313,17 @@ template <> struct Xf<4, 3> {
     y[2 * SO] = fmaf(B2, s34, A2 * s12);
     y[3 * SO] = fmaf(PB * B2, d34, fmaf(PA * A2, d12, p5));
   }
+  // the same on two channels at once (strides count 64-bit elements); operation for operation the scalar form
+  template <int SI, int SO> static __device__ __forceinline__ void at2(const uint64_t *p, uint64_t *y) {
+    const uint64_t pa = f2_pack(PA, PA), pb = f2_pack(PB, PB), a2 = f2_pack(A2, A2), b2 = f2_pack(B2, B2);
+    const uint64_t pa3 = f2_pack(PA * A2, PA * A2), pb3 = f2_pack(PB * B2, PB * B2);
+    const uint64_t p0 = p[0], p1 = p[SI], p2 = p[2 * SI], p3 = p[3 * SI], p4 = p[4 * SI], p5 = p[5 * SI];
+    const uint64_t s12 = f2_add(p1, p2), d12 = f2_sub(p1, p2), s34 = f2_add(p3, p4), d34 = f2_sub(p3, p4);
+    y[0] = f2_add(f2_add(p0, s12), s34);
+    y[SO] = f2_fma(pb, d34, f2_mul(pa, d12));
+    y[2 * SO] = f2_fma(b2, s34, f2_mul(a2, s12));
+    y[3 * SO] = f2_fma(pb3, d34, f2_fma(pa3, d12, p5));
+  }
 };
 
 // F(6,3) on the customary points (0, +-1, +-2, +-1/2, inf): B^T and A^T are dyadic, G carries the 1 / f_p factors.

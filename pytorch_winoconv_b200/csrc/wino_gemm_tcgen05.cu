@@ -527,6 +527,145 @@ __global__ void __launch_bounds__(XT_THREADS, 1) input_f43_tma_kernel(const __gr
   }
 }
 
+// ---- F(4x4,3x3) output transform with the products staged through shared memory by TMA -----------------------------
+// y = A^T M A (+ bias, ReLU) for 16-bit layers whose output channel count is a multiple of eight.  The same scheme as
+// the input side: a persistent CTA walks blocks of 8 tiles x 64 channels; one warp loads the block's 36 positions with
+// one 3-D cp.async.bulk.tensor ([64 channels, 8 tiles, 36 positions] of M) into a two-deep ring, eight warps take one
+// tile each -- lanes = the 32 channel pairs -- transform on packed fp32 pairs and store whole 128-byte runs of y.
+constexpr int YT_TILES = 8;
+constexpr int YT_C = 64;
+constexpr int YT_WARPS = 8;
+constexpr int YT_THREADS = 32 + 32 * YT_WARPS;
+template <typename TM> struct YtCfg {
+  static constexpr int BOX_BYTES = 36 * YT_TILES * YT_C * (int)sizeof(TM);
+  static constexpr int SMEM_BYTES = 2 * BOX_BYTES + 1024 + 256;
+};
+
+struct YtGeom {
+  int K, nH, nW, oH, oW;
+  int n_chb;
+  unsigned epilogue;
+  long long T, n_items;
+};
+
+template <typename TM> struct LoadPair;
+template <> struct LoadPair<float> {
+  static __device__ __forceinline__ uint64_t get(const uint8_t *p) { return *reinterpret_cast<const uint64_t *>(p); }
+};
+template <> struct LoadPair<__half> {
+  static __device__ __forceinline__ uint64_t get(const uint8_t *p) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(p));
+    return f2_pack(f.x, f.y);
+  }
+};
+template <> struct LoadPair<__nv_bfloat16> {
+  static __device__ __forceinline__ uint64_t get(const uint8_t *p) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+    return f2_pack(f.x, f.y);
+  }
+};
+
+template <typename T, typename TM>
+__global__ void __launch_bounds__(YT_THREADS, 1) output_f43_tma_kernel(const __grid_constant__ CUtensorMap map_m,
+                                                                        T *__restrict__ y, const T *__restrict__ bias,
+                                                                        const __grid_constant__ YtGeom g) {
+  using C = YtCfg<TM>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 127u) & ~127u;
+  const uint8_t *base_ptr = smem_raw + (base - raw);
+  const uint32_t bars = base + 2 * C::BOX_BYTES;   // full[2] empty[2]
+  volatile unsigned *abort_word = reinterpret_cast<volatile unsigned *>(const_cast<uint8_t *>(base_ptr) + 2 * C::BOX_BYTES + 64);
+  auto full_bar = [&](int b) { return bars + 8u * b; };
+  auto empty_bar = [&](int b) { return bars + 8u * (2 + b); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(full_bar(b), 1);
+      mbar_init(empty_bar(b), YT_WARPS);
+    }
+    *abort_word = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (long long w = blockIdx.x; w < g.n_items; w += gridDim.x, ++it) {
+        const int b = (int)(it & 1u);
+        if (!mbar_wait(empty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_word, ERR_PRODUCER_EMPTY)) break;
+        const long long tg = w / g.n_chb;
+        const int chb = (int)(w - tg * g.n_chb);
+        mbar_expect_tx(full_bar(b), (uint32_t)C::BOX_BYTES);
+        tma_load_3d(base + b * C::BOX_BYTES, &map_m, full_bar(b), chb * YT_C, (int)(tg * YT_TILES), 0);
+      }
+      if (*abort_word != 0u) {   // let the loads still in flight land before the shared memory goes away
+        for (uint32_t j = (it > 2u ? it - 2u : 0u); j < it; ++j) {
+          const long long start = clock64();
+          while (!mbar_try_wait(full_bar((int)(j & 1u)), (j >> 1) & 1u)) {
+            if (clock64() - start > WAIT_LIMIT_CLOCKS) { atomicCAS(&g_device_error, 0u, (unsigned)ERR_DRAIN); break; }
+          }
+        }
+      }
+    }
+  } else {
+    const int tl = warp - 1;               // this warp's tile of the block
+    const bool relu = (g.epilogue & WINOCONV_EPI_RELU) != 0;
+    const bool has_bias = (g.epilogue & WINOCONV_EPI_BIAS) != 0;
+    uint32_t it = 0;
+    bool alive = true;
+    for (long long w = blockIdx.x; w < g.n_items && alive; w += gridDim.x, ++it) {
+      const int b = (int)(it & 1u);
+      unsigned got = 0;
+      if (lane == 0) got = mbar_wait(full_bar(b), (it >> 1) & 1u, abort_word, ERR_MMA_FULL) ? 1u : 0u;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got == 0u) { alive = false; break; }
+      const long long tg = w / g.n_chb;
+      const int chb = (int)(w - tg * g.n_chb);
+      const long long tile = tg * YT_TILES + tl;
+      const int k = chb * YT_C + 2 * lane;
+      if (tile < g.T && k < g.K) {
+        const uint8_t *src = base_ptr + b * C::BOX_BYTES + (tl * YT_C + 2 * lane) * (int)sizeof(TM);
+        uint64_t q[36], t1[24], o[16];
+#pragma unroll
+        for (int p = 0; p < 36; ++p) q[p] = LoadPair<TM>::get(src + p * (YT_TILES * YT_C * (int)sizeof(TM)));
+#pragma unroll
+        for (int r = 0; r < 6; ++r) Xf<4, 3>::template at2<1, 1>(&q[r * 6], &t1[r * 4]);      // along W: 6 -> 4 per row
+#pragma unroll
+        for (int cidx = 0; cidx < 4; ++cidx) Xf<4, 3>::template at2<4, 4>(&t1[cidx], &o[cidx]);   // along H
+        uint64_t bv = f2_pack(0.f, 0.f);
+        if (has_bias) {
+          float bf[2];
+          VecIO<T, 2>::load(bias + k, bf);
+          bv = f2_pack(bf[0], bf[1]);
+        }
+        const unsigned t32 = (unsigned)tile;
+        const unsigned tw = t32 % (unsigned)g.nW, r2 = t32 / (unsigned)g.nW;
+        const unsigned th = r2 % (unsigned)g.nH, n = r2 / (unsigned)g.nH;
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const int oh = (int)th * 4 + a;
+          if (oh < g.oH) {
+            T *rowp = y + (((long long)n * g.oH + oh) * g.oW + (long long)tw * 4) * g.K + k;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              if ((int)tw * 4 + cc < g.oW) {
+                float f[2];
+                f2_unpack(f2_add(o[a * 4 + cc], bv), f[0], f[1]);
+                if (relu) { f[0] = fmaxf(f[0], 0.f); f[1] = fmaxf(f[1], 0.f); }
+                VecIO<T, 2>::store(rowp + (long long)cc * g.K, f);
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(b)) : "memory");
+    }
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -663,7 +802,58 @@ static cudaError_t run_input_f43_tma(const Geom &g, int dtype, const void *x, vo
   return cudaGetLastError();
 }
 
+template <typename T, typename TM>
+static cudaError_t run_output_f43_tma(const Geom &g, int product_dtype, const void *m, void *y, const void *bias,
+                                      cudaStream_t s, const char **detail) {
+  using C = YtCfg<TM>;
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { *detail = "cuTensorMapEncodeTiled unavailable"; return cudaErrorNotSupported; }
+  CUtensorMap map_m;
+  const cuuint64_t esz = sizeof(TM);
+  const cuuint64_t dims[3] = {(cuuint64_t)g.K, (cuuint64_t)g.T, 36ull};
+  const cuuint64_t st[2] = {(cuuint64_t)g.K * esz, (cuuint64_t)g.K * esz * (cuuint64_t)g.T};
+  const cuuint32_t box[3] = {(cuuint32_t)YT_C, (cuuint32_t)YT_TILES, 36u};
+  const cuuint32_t es[3] = {1u, 1u, 1u};
+  const CUtensorMapDataType dt = product_dtype == WINOCONV_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : product_dtype == WINOCONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (enc(&map_m, dt, 3, const_cast<void *>(m), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    *detail = "cuTensorMapEncodeTiled failed for the products of the F(4x4,3x3) output transform";
+    return cudaErrorInvalidValue;
+  }
+  YtGeom q;
+  q.K = g.K; q.nH = g.nH; q.nW = g.nW; q.oH = g.oH; q.oW = g.oW; q.epilogue = g.epilogue; q.T = g.T;
+  q.n_chb = (g.K + YT_C - 1) / YT_C;
+  q.n_items = ((g.T + YT_TILES - 1) / YT_TILES) * q.n_chb;
+  auto kern = output_f43_tma_kernel<T, TM>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) { *detail = "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed"; return e; }
+  const int sms = device_sm_count();
+  if (sms <= 0) { *detail = "no device"; return cudaErrorNoDevice; }
+  const unsigned grid = (unsigned)(q.n_items < sms ? q.n_items : sms);
+  kern<<<grid, YT_THREADS, C::SMEM_BYTES, s>>>(map_m, (T *)y, (const T *)bias, q);
+  return cudaGetLastError();
+}
+
 }  // namespace tc
+
+bool output_f43_tma_applies(const Geom &g, int dtype, int product_dtype, const void *m, long long t0, long long n_tiles) {
+  return (dtype == WINOCONV_F16 || dtype == WINOCONV_BF16) && (product_dtype == WINOCONV_F32 || product_dtype == dtype) &&
+         g.mD == 1 && g.mH == 4 && g.mW == 4 && g.n_pieces == 1 && g.oD == 1 && g.K % 8 == 0 &&
+         (g.epilogue & WINOCONV_EPI_POOL2) == 0 && t0 == 0 && n_tiles == g.T && g.T < (1LL << 31) &&
+         (reinterpret_cast<uintptr_t>(m) & 15u) == 0;
+}
+
+cudaError_t launch_output_f43_tma(const Geom &g, int dtype, int product_dtype, const void *m, void *y, const void *bias,
+                                  cudaStream_t s, const char **detail) {
+  *detail = "";
+  if (dtype == WINOCONV_F16) {
+    if (product_dtype == WINOCONV_F32) return tc::run_output_f43_tma<__half, float>(g, product_dtype, m, y, bias, s, detail);
+    return tc::run_output_f43_tma<__half, __half>(g, product_dtype, m, y, bias, s, detail);
+  }
+  if (product_dtype == WINOCONV_F32) return tc::run_output_f43_tma<__nv_bfloat16, float>(g, product_dtype, m, y, bias, s, detail);
+  return tc::run_output_f43_tma<__nv_bfloat16, __nv_bfloat16>(g, product_dtype, m, y, bias, s, detail);
+}
 
 bool input_f43_tma_applies(const Geom &g, int dtype, const void *x, long long t0, long long n_tiles) {
   return (dtype == WINOCONV_F16 || dtype == WINOCONV_BF16) && g.mD == 1 && g.mH == 4 && g.mW == 4 && g.n_pieces == 1 &&

@@ -35,6 +35,11 @@ cudaError_t launch_gemm_tf32(int split, int positions, long long tiles, int c_pa
 bool input_f43_tma_applies(const Geom &g, int dtype, const void *x, long long t0, long long n_tiles);
 cudaError_t launch_input_f43_tma(const Geom &g, int dtype, const void *x, void *v, cudaStream_t s, const char **detail);
 
+// The matching output transform (output channels a multiple of eight, bias / ReLU epilogue, one pass over all tiles).
+bool output_f43_tma_applies(const Geom &g, int dtype, int product_dtype, const void *m, long long t0, long long n_tiles);
+cudaError_t launch_output_f43_tma(const Geom &g, int dtype, int product_dtype, const void *m, void *y, const void *bias,
+                                  cudaStream_t s, const char **detail);
+
 // Fused F(2x2,3x3) path (f16 / bf16): transformed filter u [16][K][R], then one kernel for the whole layer.
 cudaError_t launch_fused_filter_transform(const FGeom &g, int dtype, const void *w, void *u, cudaStream_t s);
 cudaError_t launch_fused_forward(const FGeom &g, int dtype, const void *x, const void *u, const void *bias, void *y,
