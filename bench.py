@@ -529,9 +529,10 @@ def run_ours(args):
         global_batch = args.batch or 256
         batch = shard_of(global_batch)
         ws = [w.to(dev) for w in vgg_weights(torch.float16)]
-        fused = args.algo in ("auto", "row", "fused")
-        algo_code = {"auto": capi.ALGO_ROW, "row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
-        model = engine.VGG16ConvStack(ws, batch, tile_m=2 if fused else 4, algo=algo_code,
+        fused = args.algo in ("row", "fused")
+        algo_code = {"auto": capi.ALGO_AUTO, "row": capi.ALGO_ROW, "fused": capi.ALGO_FUSED, "staged": capi.ALGO_STAGED}[args.algo]
+        # auto: the library's own choice per layer (tile_m = 0)
+        model = engine.VGG16ConvStack(ws, batch, tile_m=0 if args.algo == "auto" else (2 if fused else 4), algo=algo_code,
                                       product_dtype=torch.float16 if (args.product == "f16" and not fused) else None)
         x_host = torch.rand(batch, 224, 224, 3, generator=g).half().pin_memory()
         layers = model.layers
@@ -771,32 +772,44 @@ def run_ours(args):
                           "roof_frac_contract": round(max(t_tc_c, t_hbm_c) / t_ms, 4)})
         h = out
     stage_tot = [sum(l["stage_ms"][i] for l in per_layer) for i in range(3)]
-    dom = max(range(3), key=lambda i: stage_tot[i])
-    algos = [int(c.info.algo) for c in layers]
-    is_fused = all(a in (capi.ALGO_FUSED, capi.ALGO_ROW) for a in algos)
-    is_row = all(a == capi.ALGO_ROW for a in algos)
-    # fused paths: one dominant-kernel launch per layer (a layer that needs the channel-padding or phase-gather
-    # pass adds a small launch, timed with it)
-    n_dom_launch = len(per_layer) if is_fused else sum(l["launches"] // 3 for l in per_layer)
+    # Time per kernel class over the step (a stack may mix algorithms: AUTO takes staged F(4x4,3x3) for some layers and
+    # the row-piece kernel for the rest): the dominant class is the one the roofline object describes.
     esz = x_host.element_size()
-    if dom == 1:
-        alg = sum(c.info.gemm_flops for c in layers)
-        achieved = alg / (stage_tot[1] * 1e-3) / 1e12
+    classes = {}      # kernel -> [ms, launches, algorithmic flops, algorithmic bytes]
+
+    def add(kernel, ms, flops=0.0, nbytes=0.0, launches=1):
+        c = classes.setdefault(kernel, [0.0, 0, 0.0, 0.0])
+        c[0] += ms; c[1] += launches; c[2] += flops; c[3] += nbytes
+
+    for l, conv in zip(per_layer, layers):
+        a = int(conv.info.algo)
+        if a == capi.ALGO_ROW:
+            add("rowfused_kernel", l["stage_ms"][1], flops=conv.info.gemm_flops)
+        elif a == capi.ALGO_FUSED:
+            add("fused23_kernel", l["stage_ms"][1], flops=conv.info.gemm_flops)
+        else:
+            passes = max(l["launches"] // 3, 1)
+            f43_16 = io_dtype != torch.float32 and max(int(v) for v in conv.info.tile_m) == 4
+            add("input_f43_tma_kernel" if f43_16 else "input_transform_kernel", l["stage_ms"][0],
+                nbytes=float(esz) * math.prod(conv.in_shape), launches=passes)      # it must read x once
+            if io_dtype == torch.float32:
+                add("gemm_simt_kernel" if product_peak(conv)[1] == "fp32-fma" else "gemm_persistent_kernel",
+                    l["stage_ms"][1], flops=conv.info.gemm_flops, launches=passes)
+            else:
+                add("gemm_persistent_kernel", l["stage_ms"][1], flops=conv.info.gemm_flops, launches=passes)
+            add("output_f43_tma_kernel" if f43_16 and not (int(conv.desc.epilogue) & capi.EPI_POOL2) else "output_transform_kernel",
+                l["stage_ms"][2], nbytes=float(esz) * math.prod(conv.out_shape), launches=passes)   # it must write y once
+    kernel = max(classes, key=lambda k_: classes[k_][0])
+    dom_ms, n_dom_launch, dom_flops, dom_bytes = classes[kernel]
+    if dom_flops > 0:
+        achieved = dom_flops / (dom_ms * 1e-3) / 1e12
         if io_dtype == torch.float32:
             peak, bound = product_peak(layers[0])
             unit = "TFLOP/s"
-            kernel = "gemm_simt_kernel" if bound == "fp32-fma" else "gemm_persistent_kernel"
         else:
             peak, unit, bound = tc_peak_16, "TFLOP/s", "tensor"
-            kernel = "rowfused_kernel" if is_row else ("fused23_kernel" if is_fused else "gemm_persistent_kernel")
     else:
-        if dom == 0:   # algorithmic bytes of the input transform: it must read x once
-            alg = sum(float(esz) * math.prod(c.in_shape) for c in layers)
-            kernel = "input_transform_kernel"
-        else:          # the output transform must write y once
-            alg = sum(float(esz) * math.prod(c.out_shape) for c in layers)
-            kernel = "output_transform_kernel"
-        achieved = alg / (stage_tot[dom] * 1e-3) / 1e9
+        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
         peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
     traffic, traffic_source = None, None
     if (args.workload, kernel) in NCU_TRAFFIC_PER_IMAGE:
@@ -811,7 +824,8 @@ def run_ours(args):
                                       "(x + w + convolution output bytes) / HBM peak), divided by the layers' measured time",
                 "traffic": traffic, "traffic_source": traffic_source,
                 "kernel": kernel, "launches_per_step": n_dom_launch,
-                "avg_launch_us": round(1e3 * stage_tot[dom] / max(n_dom_launch, 1), 2),
+                "avg_launch_us": round(1e3 * dom_ms / max(n_dom_launch, 1), 2),
+                "kernel_share": {k_: round(v[0] / sum(c[0] for c in classes.values()), 4) for k_, v in classes.items()},
                 "peak_source": f"MEASURED_PEAKS.json ({peaks_kind}; {'burst' if single_layer else 'sustained'} bf16 figure, copy bandwidth)",
                 "stage_share": {n: round(t / sum(stage_tot), 4) for n, t in zip(stage_names, stage_tot)}}
 

@@ -58,7 +58,10 @@ typedef enum winoconv_gemm {
 } winoconv_gemm_t;
 
 typedef enum winoconv_algo {
-  WINOCONV_ALGO_AUTO = 0,   /* ROW where it applies, else FUSED where it applies, else STAGED            */
+  WINOCONV_ALGO_AUTO = 0,   /* ROW where it applies, else FUSED where it applies, else STAGED; with      */
+                            /* tile_m = 0 a 16-bit 3x3 stride-1 layer of >= 512 input and output channels */
+                            /* whose 4-wide tiles cover the output exactly (>= 4096 of them) runs as       */
+                            /* STAGED F(4x4,3x3) instead (measured faster; needs the V / M scratch)        */
   WINOCONV_ALGO_STAGED = 1, /* input transform -> batched GEMM -> output transform through V / M scratch  */
   WINOCONV_ALGO_FUSED = 2,  /* one tcgen05 kernel, 3x3 pieces as F(2x2,3x3); f16 / bf16, any stride       */
   WINOCONV_ALGO_ROW = 3     /* one tcgen05 kernel, 1x3 pieces: F(2,3) along W, taps along H / depth summed */

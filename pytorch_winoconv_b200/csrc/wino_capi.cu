@@ -102,8 +102,20 @@ int build_plan(const winoconv_desc_t *d, Plan *plan) {
   const bool f43_ok = ks[0] == 1 && in[0] == 1 && ks[1] == 3 && ks[2] == 3 && st[1] == 1 && st[2] == 1;
   const bool single_kernel_candidate = d->dtype != WINOCONV_F32 && d->algo != WINOCONV_ALGO_STAGED &&
                                        d->gemm_engine != WINOCONV_GEMM_SIMT && d->product_dtype == WINOCONV_F32;
+  // Where F(4x4,3x3) pays for its intermediates: at 512 -> 512 channels the contraction outweighs the V and M traffic,
+  // and with the tiles covering the output exactly and enough of them to fill the GPU the staged flow beats the
+  // row-piece kernel (measured on B200, 512 -> 512 at 28 x 28, N = 256: 0.60 ms against 0.70 ms; at 14 x 14, where 4-wide
+  // tiles cover 16 x 16, 0.23 against 0.18 ms; 256 -> 256 at 56 x 56: 1.03 against 0.69 ms).  AUTO takes it there, within
+  // the same 2e-2 bound (E_B 1.2e-2 against 2.8e-3).  WINOCONV_AUTO_F43=0 keeps the row-piece kernel everywhere.
+  static const int auto_f43_env = [] { const char *v = getenv("WINOCONV_AUTO_F43"); return v && *v ? atoi(v) : 1; }();
+  bool f43_wins = false;
+  if (f43_ok && single_kernel_candidate && d->algo == WINOCONV_ALGO_AUTO && d->tile_m == 0 && auto_f43_env != 0 &&
+      d->gemm_engine != WINOCONV_GEMM_SIMT && d->c_in >= 512 && d->k_out >= 512 && d->c_in % 8 == 0 && d->k_out % 8 == 0) {
+    const int oh = in[1] + 2 * pd[1] - 2, ow = in[2] + 2 * pd[2] - 2;
+    f43_wins = oh > 0 && ow > 0 && oh % 4 == 0 && ow % 4 == 0 && (long long)d->batch * (oh / 4) * (ow / 4) >= 4096;
+  }
   int tile_m = d->tile_m;
-  if (tile_m == 0) tile_m = (f43_ok && !single_kernel_candidate) ? 4 : 2;
+  if (tile_m == 0) tile_m = (f43_ok && (!single_kernel_candidate || f43_wins)) ? 4 : 2;
   if (tile_m != 2 && tile_m != 4 && tile_m != 6) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m must be 0, 2, 4 or 6");
   if (tile_m == 4 && !f43_ok) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 4 is F(4x4,3x3): 2-D, 3x3 kernel, stride 1 only");
   if (tile_m == 6 && !f43_ok) return fail(WINOCONV_ERR_UNSUPPORTED, "tile_m = 6 is F(6x6,3x3): 2-D, 3x3 kernel, stride 1 only");

@@ -51,6 +51,24 @@ def test_plan_matches_hand_computed_figures(name, kw, expect):
     assert info.algo == capi.ALGO_STAGED
 
 
+def test_auto_takes_f43_where_it_was_measured_to_win():
+    """AUTO on a 16-bit 3x3 stride-1 layer: the row-piece kernel, except 512 -> 512 channels with 4-wide tiles that cover
+    the output exactly and at least 4096 of them -- there staged F(4x4,3x3) (36 positions, V and M scratch)."""
+    def plan(n, c, k, hw, **kw):
+        return capi.plan(capi.make_desc(ndim=2, batch=n, c_in=c, k_out=k, in_size=(hw, hw), ker_size=3, pad=1, **kw))
+    big = plan(256, 512, 512, 28)
+    assert big.algo == capi.ALGO_STAGED and big.positions == 36 and list(big.tile_m) == [1, 4, 4] and big.tiles == 256 * 49
+    assert big.input_ws_bytes == 36 * 256 * 49 * 512 * 2 and big.product_ws_bytes == 36 * 256 * 49 * 512 * 4
+    for n, c, k, hw in ((32, 512, 512, 28),       # too few tiles to fill the GPU
+                        (256, 512, 512, 14),      # 4-wide tiles would cover 16 x 16
+                        (256, 256, 512, 28),      # fewer input channels
+                        (256, 256, 256, 56)):
+        i = plan(n, c, k, hw)
+        assert i.algo == capi.ALGO_ROW and i.positions == 4 and i.input_ws_bytes == 0, (n, c, k, hw)
+    assert plan(256, 512, 512, 28, tile_m=2).algo == capi.ALGO_ROW          # an explicit tile keeps its algorithm
+    assert plan(256, 512, 512, 28, algo=capi.ALGO_ROW).algo == capi.ALGO_ROW
+
+
 @pytest.mark.parametrize("kw,windows,tiles", [
     (dict(ndim=2, batch=64, c_in=3, k_out=64, in_size=(224, 224), ker_size=7, stride=2, pad=3), 9, 64 * 56 * 56),
     (dict(ndim=2, batch=32, c_in=128, k_out=128, in_size=(56, 56), ker_size=5, pad=2), 4, 32 * 28 * 28),

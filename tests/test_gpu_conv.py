@@ -249,6 +249,27 @@ def test_cfg1_fp32_product_arithmetic_table():
         assert table[("tf32", tm)] <= 2e-2          # bounded, but (measured) over the fp32 tolerance
 
 
+def test_auto_f43_on_a_512_channel_layer():
+    """The one place AUTO leaves the row-piece kernel: 512 -> 512 at 28 x 28 with >= 4096 tiles runs as staged
+    F(4x4,3x3) with both transforms staged through shared memory by TMA.  Checked against the float64 direct
+    convolution on the first and the last image (the whole batch would take the CPU minutes)."""
+    n = 84                                             # 84 x 49 = 4116 tiles
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(n, 512, 28, 28, generator=g).half()
+    w = wo.kaiming_normal((512, 512, 3, 3), 6).half()
+    b = seeded((512,), 7, dtype=torch.float16)
+    y, conv = run_engine(x, w, padding=1, bias=b, relu=True)
+    assert conv.info.algo == capi.ALGO_STAGED and conv.info.positions == 36 and conv.launches_per_call == 3
+    for i in (0, n - 1):
+        o = torch.relu(wo.direct_conv_f64(x[i:i + 1], w, padding=1) + b.double().view(1, -1, 1, 1))
+        err = wo.error_metrics(y[i:i + 1], o)
+        print("AUTO -> F(4x4,3x3), image", i, err)
+        assert err["E_B"] <= TOL[torch.float16], err
+    y2, conv2 = run_engine(x[:8], w, padding=1, bias=b, relu=True)       # a small batch stays on the row-piece kernel
+    assert conv2.info.algo == capi.ALGO_ROW
+    assert wo.error_metrics(y2, y[:8].double())["E_A"] < 2e-2            # the two algorithms agree to fp16 accuracy
+
+
 F63_CASES = [
     # N, C, K, spatial, padding
     (2, 8, 8, (12, 12), 1),            # 2 x 2 whole tiles
