@@ -81,8 +81,9 @@ class WinoConv:
     """A planned forward convolution with its transformed filter resident on the device.
 
     weight: ``[K, C, (kD,) kH, kW]`` (torch order).  ``in_shape`` is the channels-last input
-    shape.  ``tile_m``: 0 auto (2-wide tiles where a single-kernel path takes the layer -- every 16-bit
-    layer -- else F(4x4,3x3) for 2-D 3x3 stride 1 and F(2,r) pieces otherwise), 2, 4, or 6 (F(6x6,3x3), fp32 layers only).
+    shape.  ``tile_m``: 0 auto (2-wide tiles where a single-kernel path takes the layer -- 16-bit layers, except
+    3x3 stride-1 layers of >= 512 -> >= 512 channels with >= 4096 exactly-covering 4-wide tiles, which run as staged
+    F(4x4,3x3) -- else F(4x4,3x3) for 2-D 3x3 stride 1 and F(2,r) pieces otherwise), 2, 4, or 6 (F(6x6,3x3), fp32 layers only).
     """
 
     def __init__(self, in_shape: Sequence[int], weight: torch.Tensor, *, stride=1, padding=0, tile_m: int = 0,
