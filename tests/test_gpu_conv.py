@@ -249,6 +249,24 @@ def test_cfg1_fp32_product_arithmetic_table():
         assert table[("tf32", tm)] <= 2e-2          # bounded, but (measured) over the fp32 tolerance
 
 
+@pytest.mark.parametrize("dtype,product", [(torch.bfloat16, None), (torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16)])
+@pytest.mark.parametrize("n,c,k,sp,pad", [(3, 64, 72, (20, 24), 1),       # whole tiles, K not a multiple of 64
+                                          (2, 136, 64, (30, 27), 1),      # ragged tiles in both directions, three channel blocks
+                                          (1, 8, 8, (9, 41), 0)])         # no padding, one channel vector, a wide strip
+def test_staged_f43_tma_transforms(dtype, product, n, c, k, sp, pad):
+    """F(4x4,3x3) with both transforms staged through shared memory by TMA (channels a multiple of eight), in the
+    dtype and product combinations the BASELINE configurations do not reach; bias and ReLU in the output transform."""
+    x = seeded((n, c) + sp, 41, dtype=dtype)
+    w = wo.kaiming_normal((k, c, 3, 3), 42).to(dtype)
+    b = seeded((k,), 43, dtype=dtype)
+    y, conv = run_engine(x, w, padding=pad, tile_m=4, bias=b, relu=True, product_dtype=product)
+    assert conv.info.algo == capi.ALGO_STAGED and conv.info.positions == 36
+    o = torch.relu(wo.direct_conv_f64(x, w, padding=pad) + b.double().view(1, -1, 1, 1))
+    err = wo.error_metrics(y, o)
+    tol = {torch.float16: 3e-2, torch.bfloat16: 1.6e-1}[dtype]     # 16-bit products on top of the 16-bit operands
+    assert err["E_B"] <= tol, err
+
+
 def test_auto_f43_on_a_512_channel_layer():
     """The one place AUTO leaves the row-piece kernel: 512 -> 512 at 28 x 28 with >= 4096 tiles runs as staged
     F(4x4,3x3) with both transforms staged through shared memory by TMA.  Checked against the float64 direct
